@@ -85,9 +85,10 @@ typedef struct MsaFmhaParams {
   int64_t v_stride_page, v_stride_head, v_stride_tok;
   int64_t out_stride_tok, out_stride_head;
   int64_t kbi_stride_tok, kbi_stride_head;
+  int64_t kv_extent;       /* outermost extent of k / v: total keys (ragged) or pages in the pool */
   int32_t total_q, num_qo_heads, num_kv_heads, batch;
   int32_t num_work;        /* dense: work items; sparse: ignored                             */
-  int32_t block_m;         /* 16, 64 or 128 packed rows per item                             */
+  int32_t block_m;         /* 16, 64, 128 packed rows per item; 256 selects the tcgen05 kernel */
   int32_t pack;            /* query heads folded into the row dimension (1 or Hq/Hkv)        */
   int32_t page_size;       /* 0 = ragged K/V                                                 */
   int32_t kv_block_num;    /* sparse: entries per (token, kv head)                           */
@@ -142,7 +143,7 @@ typedef struct MsaPlanArgs {
   const int32_t* qo_offset;   /* [B] host */
   int32_t batch;
   int32_t num_qo_heads, num_kv_heads;
-  int32_t block_m;            /* 16 / 64 / 128 */
+  int32_t block_m;            /* 16 / 64 / 128 / 256 */
   int32_t pack;               /* 1 or Hq/Hkv   */
   int32_t num_splits;         /* >=1 fixed; <=0 adaptive with -num_splits as the ceiling */
   int32_t num_sms;            /* device SM count (adaptive mode target)  */

@@ -55,7 +55,7 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
 extern "C" int msa_plan_dense(const MsaPlanArgs* a, MsaWorkItem* work, int32_t capacity, int32_t* splits_per_row,
                               int32_t* max_splits_out) {
   if (!a || !a->qo_len || !a->kv_len || !a->qo_offset || (!work && capacity > 0)) return MSA_ERR_BAD_ARG;
-  if (a->block_m != 16 && a->block_m != 64 && a->block_m != 128) return MSA_ERR_BAD_ARG;
+  if (a->block_m != 16 && a->block_m != 64 && a->block_m != 128 && a->block_m != 256) return MSA_ERR_BAD_ARG;
   if (a->num_qo_heads <= 0 || a->num_kv_heads <= 0 || a->num_qo_heads % a->num_kv_heads) return MSA_ERR_BAD_ARG;
   const int G = a->pack;
   if (G < 1 || (a->num_qo_heads / a->num_kv_heads) % G || G > a->block_m) return MSA_ERR_BAD_ARG;

@@ -1,7 +1,457 @@
-// tcgen05 / TMEM FMHA forward (placeholder selection hook until the kernel lands).
-#include "common.cuh"
+// Dense causal FMHA forward on the 5th-generation tensor cores (tcgen05 + TMEM) for sm_100a.
+//
+// Serves the prefill shapes of `fmha_sail` (upstream dense/paged mainloop,
+// csrc/include/sm80_fmha_fwd_mainloop.hpp:262-636): bf16 Q/K/V, head_dim 128, ragged K/V or
+// pages of 128 keys, one query head per row tile, optional per-tile max-score and LSE output.
+//
+// One CTA = 256 consecutive query rows of one (batch item, head) = two 128-row Q tiles "A" and
+// "B" that walk the same KV tiles, so every K/V tile in shared memory feeds two MMAs and the
+// softmax of one Q tile overlaps the tensor-core work of the other.
+//
+//   warp 0      TMA producer: Q once, then K and V tiles (2-deep rings each) by
+//               cp.async.bulk.tensor with the physical page as a run-time coordinate
+//   warp 1      MMA issuer (one elected lane): S = Q K^T into TMEM, O += P V with P read from
+//               TMEM; completion is signalled to mbarriers with tcgen05.commit
+//   warps 2-5   softmax of tile A: thread r owns row r (TMEM lane r): mask, row max, optional
+//   warps 6-9   softmax of tile B  max-score store, exp2, bf16 P written back over S, lazy
+//               rescale of O, final normalise + store
+//
+// TMEM (512 columns): S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P aliases the
+// first 64 columns of its S.  Shared memory: Q 64 KB, K 2x32 KB, V 2x32 KB, all in the
+// 128-byte-swizzled layout that both TMA and the UMMA descriptors understand.
+//
+// Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, reports
+// MSA_STATUS_TIMEOUT in the status word, releases its TMEM and exits.
+#include <mutex>
+
+#include "tc_ptx.cuh"
 
 namespace msa {
-int fmha_tc_supported(const MsaFmhaParams&) { return 0; }
-int fmha_tc_launch(const MsaFmhaParams&, cudaStream_t) { return MSA_ERR_UNSUPPORTED; }
+namespace tc {
+namespace {
+
+constexpr int BM = 128;                 // rows per Q tile
+constexpr int BN = 128;                 // keys per KV tile
+constexpr int SUB_BYTES = BM * 64 * 2;  // one [128 rows][64 bf16] swizzled sub-tile
+constexpr int TILE_BYTES = 2 * SUB_BYTES;
+constexpr int KSTAGES = 2, VSTAGES = 2;
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
+constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
+constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // + alignment slack
+constexpr int NTHREADS = 320;
+constexpr float kRescaleThreshold = 8.0f;          // log2 units: P stays <= 2^8
+
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13,
+           V_FIX = 15, NUM_BARS = 16 };
+
+struct Knobs {            // descriptor constants (bytes)
+  uint32_t k_lbo, k_sbo, v_lbo, v_sbo, v_kstep, p_colstep;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+               const Knobs kn) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base + OFF_BAR;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
+  auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---------------- work item ----------------
+  const MsaWorkItem w = p.work[blockIdx.x];
+  const int b = w.batch, head = w.head0, row0 = w.row0;
+  const int h_r = p.num_qo_heads / p.num_kv_heads;
+  const int kvh = head / h_r;
+  const int qo_base = p.qo_start[b];
+  const int ql = p.qo_start[b + 1] - qo_base;
+  const int kv_len = p.kv_len[b];
+  const int off = p.qo_offset[b];
+  const bool paged = p.page_size > 0;
+  int n_tiles[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int m0 = row0 + x * BM;
+    if (m0 >= ql) { n_tiles[x] = 0; continue; }
+    const int last = min(m0 + BM, ql) - 1;
+    long long vis = min(static_cast<long long>(kv_len), static_cast<long long>(last) + off + 1);
+    if (vis < 0) vis = 0;
+    n_tiles[x] = min(w.kv_tile_end, static_cast<int>((vis + BN - 1) / BN));
+  }
+  const int n_total = max(n_tiles[0], n_tiles[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(K_FULL + s), 1);  mbar_init(bar(K_EMPTY + s), 1);
+      mbar_init(bar(V_FULL + s), 1);  mbar_init(bar(V_EMPTY + s), 1);
+      mbar_init(bar(S_FULL + s), 1);  mbar_init(bar(P_FULL + s), BM);
+      mbar_init(bar(O_FULL + s), 1);
+    }
+    mbar_init(bar(V_FIX), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar(Q_FULL), 2 * TILE_BYTES);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf)
+          tma_load_3d(smem_base + OFF_Q + x * TILE_BYTES + hlf * SUB_BYTES, &tm_q, bar(Q_FULL), hlf * 64, head,
+                      qo_base + row0 + x * BM);
+    }
+    const int page_base = paged ? p.kv_page_indptr[b] : 0;
+    const int kv_base = paged ? 0 : p.kv_start[b];
+    uint32_t fix_phase = 0;
+    bool alive = true;
+    for (int j = 0; j < n_total && alive; ++j) {
+      const int ks = j % KSTAGES, vs = j % VSTAGES;
+      const int page = paged ? p.kv_indices[page_base + j] : 0;
+      const int valid_rows = min(BN, kv_len - j * BN);
+      const bool fix = valid_rows < BN;                 // tail tile: rows past kv_len must read as 0 in V
+      if (lane == 0) {
+        alive = mbar_wait(bar(K_EMPTY + ks), ((j / KSTAGES) & 1) ^ 1, abort_flag);
+        if (alive) {
+          mbar_arrive_expect_tx(bar(K_FULL + ks), TILE_BYTES);
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const uint32_t dst = smem_base + OFF_K + ks * TILE_BYTES + hlf * SUB_BYTES;
+            if (paged) tma_load_4d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, 0, kvh, page);
+            else tma_load_3d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, kvh, kv_base + j * BN);
+          }
+          alive = mbar_wait(bar(V_EMPTY + vs), ((j / VSTAGES) & 1) ^ 1, abort_flag);
+        }
+        if (alive) {
+          const uint32_t vbar = fix ? bar(V_FIX) : bar(V_FULL + vs);
+          mbar_arrive_expect_tx(vbar, TILE_BYTES);
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const uint32_t dst = smem_base + OFF_V + vs * TILE_BYTES + hlf * SUB_BYTES;
+            if (paged) tma_load_4d(dst, &tm_v, vbar, hlf * 64, 0, kvh, page);
+            else tma_load_3d(dst, &tm_v, vbar, hlf * 64, kvh, kv_base + j * BN);
+          }
+        }
+      }
+      alive = __shfl_sync(0xffffffffu, alive, 0);
+      if (fix && alive) {
+        alive = mbar_wait(bar(V_FIX), fix_phase, abort_flag);
+        alive = __all_sync(0xffffffffu, alive);
+        fix_phase ^= 1;
+        if (alive) {
+          // whole 128-byte rows are zeroed, so the swizzle does not matter
+          unsigned char* vt = smem_gen + OFF_V + vs * TILE_BYTES;
+          for (int c = lane; c < (BN - valid_rows) * 16; c += 32) {
+            const int r = valid_rows + (c >> 4), ch = c & 15;
+            *reinterpret_cast<uint4*>(vt + (ch >> 3) * SUB_BYTES + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(V_FULL + vs));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false, false);
+      constexpr uint32_t IDESC_PV = idesc_bf16(BM, kHeadDim, false, true);
+      bool alive = n_total > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag) : true;
+      auto issue_qk = [&](int x, int j) {
+        const int ks = j % KSTAGES;
+        const uint32_t qa = smem_base + OFF_Q + x * TILE_BYTES, ka = smem_base + OFF_K + ks * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t o = (k >> 2) * SUB_BYTES + (k & 3) * 32;
+          mma_ss(tmem + x * BN, smem_desc(qa + o, kn.k_lbo, kn.k_sbo), smem_desc(ka + o, kn.k_lbo, kn.k_sbo),
+                 IDESC_QK, k > 0);
+        }
+      };
+      auto issue_pv = [&](int x, int j) {
+        const int vs = j % VSTAGES;
+        const uint32_t va = smem_base + OFF_V + vs * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_ts(tmem + 256 + x * kHeadDim, tmem + x * BN + k * kn.p_colstep,
+                 smem_desc(va + k * kn.v_kstep, kn.v_lbo, kn.v_sbo), IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+      };
+      if (alive && n_total > 0) {
+        alive = mbar_wait(bar(K_FULL + 0), 0, abort_flag);
+        if (alive) {
+          tc_fence_after();
+#pragma unroll
+          for (int x = 0; x < 2; ++x)
+            if (n_tiles[x] > 0) { issue_qk(x, 0); mma_commit(bar(S_FULL + x)); }
+          mma_commit(bar(K_EMPTY + 0));
+        }
+      }
+      for (int j = 0; j < n_total && alive; ++j) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (j >= n_tiles[x] || !alive) continue;
+          alive = mbar_wait(bar(P_FULL + x), j & 1, abort_flag);
+          if (alive) alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag);
+          if (!alive) break;
+          tc_fence_after();
+          issue_pv(x, j);
+          if (j + 1 < n_tiles[x]) {
+            alive = mbar_wait(bar(K_FULL + (j + 1) % KSTAGES), ((j + 1) / KSTAGES) & 1, abort_flag);
+            if (!alive) break;
+            tc_fence_after();
+            issue_qk(x, j + 1);
+            mma_commit(bar(S_FULL + x));
+          } else {
+            mma_commit(bar(O_FULL + x));
+          }
+        }
+        if (!alive) break;
+        mma_commit(bar(V_EMPTY + j % VSTAGES));
+        if (j + 1 < n_total) mma_commit(bar(K_EMPTY + (j + 1) % KSTAGES));
+      }
+    }
+  } else {
+    // =========================== softmax / epilogue ===========================
+    const int x = (warp - 2) >> 2;                       // 0: tile A, 1: tile B
+    const int r = ((warp & 3) << 5) | lane;              // row in tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
+    const uint32_t tS = tmem + x * BN + lane_addr;
+    const uint32_t tO = tmem + 256 + x * kHeadDim + lane_addr;
+    const int m0 = row0 + x * BM;
+    const int i = m0 + r;                                // token index within the sequence
+    const bool row_ok = i < ql;
+    const int gtok = qo_base + i;
+    const int lim = row_ok ? min(i + off, kv_len - 1) : -1;
+    const int nx = n_tiles[x];
+    const float scale_log2 = p.sm_scale * kLog2e * (p.k_scale_head ? p.k_scale_head[kvh] : 1.f);
+    const bool want_score = (p.flags & MSA_FLAG_OUT_SCORE) != 0 && p.max_score != nullptr;
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool alive = true;
+
+    for (int j = 0; j < nx && alive; ++j) {
+      alive = mbar_wait(bar(S_FULL + x), j & 1, abort_flag);
+      if (!alive) break;
+      tc_fence_after();
+      const int pos0 = j * BN;
+      const bool need_mask = (pos0 + BN - 1 > m0 + off) || (pos0 + BN > kv_len);
+      // ---- pass 1: row max of the raw scores ----
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + c * 32, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (pos0 + c * 32 + e <= lim) mx = fmaxf(mx, __uint_as_float(v[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+        }
+      }
+      if (want_score && row_ok && j < p.max_k_tiles) {
+        const int64_t o = (static_cast<int64_t>(head) * p.max_k_tiles + j) * p.total_q + gtok;
+        if (p.max_score_dtype == MSA_DT_BF16) static_cast<__nv_bfloat16*>(p.max_score)[o] = __float2bfloat16_rn(mx);
+        else static_cast<float*>(p.max_score)[o] = mx;
+      }
+      // ---- running max with lazy rescale ----
+      const float m_cand = fmaxf(m_used, mx * scale_log2);
+      const bool bump = (m_cand - m_used) > kRescaleThreshold;      // false for (-inf) - (-inf) = NaN
+      float factor = 1.f;
+      if (bump) { factor = exp2_fast(m_used - m_cand); m_used = m_cand; l_sum *= factor; }
+      if (j > 0 && __any_sync(0xffffffffu, bump)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tO + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+          tmem_st32(tO + c * 32, v);
+        }
+      }
+      const float msafe = (m_used == -INFINITY) ? 0.f : m_used;
+      // ---- pass 2: P = exp2(S * scale - m), bf16, written over the first half of S ----
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = exp2_fast(fmaf(__uint_as_float(v[e]), scale_log2, -msafe));
+          float p1 = exp2_fast(fmaf(__uint_as_float(v[e + 1]), scale_log2, -msafe));
+          if (need_mask) {
+            if (pos0 + c * 32 + e > lim) p0 = 0.f;
+            if (pos0 + c * 32 + e + 1 > lim) p1 = 0.f;
+          }
+          l_sum += p0 + p1;
+          pk[e >> 1] = pack2<false>(p0, p1);
+        }
+        tmem_st16(tS + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(P_FULL + x));
+    }
+
+    // ---- epilogue ----
+    if (alive && nx > 0) alive = mbar_wait(bar(O_FULL + x), 0, abort_flag);
+    if (alive) {
+      tc_fence_after();
+      const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
+      const float inv = l_sum > 0.f ? p.out_scale * vsh / l_sum : 0.f;
+      __nv_bfloat16* dst = p.out ? static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(gtok) * p.out_stride_tok +
+                                       static_cast<int64_t>(head) * p.out_stride_head
+                                 : nullptr;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        if (nx > 0) {
+          tmem_ld32(tO + c * 32, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
+        }
+        if (row_ok && dst) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 o4;
+            o4.x = pack2<false>(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
+            o4.y = pack2<false>(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+            o4.z = pack2<false>(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
+            o4.w = pack2<false>(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + e) = o4;
+          }
+        }
+      }
+      if (row_ok && p.lse)
+        p.lse[static_cast<int64_t>(gtok) * p.num_qo_heads + head] =
+            l_sum > 0.f ? m_used * kLn2 + __logf(l_sum) : -INFINITY;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0 && p.status) atomicExch(p.status, MSA_STATUS_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// rank-n bf16 map with a 128-byte swizzle; dims/strides innermost first, strides in bytes for dims 1..n-1
+bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+              const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gd[5]; cuuint64_t gs[4]; cuuint32_t bx[5]; cuuint32_t es[5];
+  for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gd, gs, bx, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+Knobs g_knobs = {16, 1024, 16384, 1024, 2048, 8};
+
+}  // namespace
+
+}  // namespace tc
+
+// Shapes the tcgen05 kernel takes; everything else runs on the mma.sync kernel.
+int fmha_tc_supported(const MsaFmhaParams& p) {
+  if (p.block_m != 256) return 0;
+  return 1;
+}
+
+int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
+  using namespace tc;
+  if (p.q_dtype != MSA_DT_BF16 || p.kv_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
+  if ((p.flags & MSA_FLAG_SPARSE) || !(p.flags & MSA_FLAG_OUT_O) || p.partial_o || p.pack != 1) return MSA_ERR_UNSUPPORTED;
+  if (p.page_size != 0 && p.page_size != BN) return MSA_ERR_UNSUPPORTED;
+  if (!p.out || !p.v) return MSA_ERR_BAD_ARG;
+  if (p.num_work <= 0) return MSA_OK;
+
+  CUtensorMap tq, tk, tv;
+  {
+    const uint64_t dims[3] = {128, static_cast<uint64_t>(p.num_qo_heads), static_cast<uint64_t>(p.total_q)};
+    const uint64_t str[2] = {static_cast<uint64_t>(p.q_stride_head) * 2, static_cast<uint64_t>(p.q_stride_tok) * 2};
+    const uint32_t box[3] = {64, 1, BM};
+    if (!make_map(&tq, p.q, 3, dims, str, box)) return MSA_ERR_LAUNCH;
+  }
+  if (p.kv_extent <= 0) return MSA_ERR_BAD_ARG;
+  const uint64_t big = static_cast<uint64_t>(p.kv_extent);   // rows / pages past it read as zero
+  if (p.page_size > 0) {
+    const uint64_t dims[4] = {128, BN, static_cast<uint64_t>(p.num_kv_heads), big};
+    const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * 2, static_cast<uint64_t>(p.k_stride_head) * 2,
+                            static_cast<uint64_t>(p.k_stride_page) * 2};
+    const uint64_t vs[3] = {static_cast<uint64_t>(p.v_stride_tok) * 2, static_cast<uint64_t>(p.v_stride_head) * 2,
+                            static_cast<uint64_t>(p.v_stride_page) * 2};
+    const uint32_t box[4] = {64, BN, 1, 1};
+    if (!make_map(&tk, p.k, 4, dims, ks, box) || !make_map(&tv, p.v, 4, dims, vs, box)) return MSA_ERR_LAUNCH;
+  } else {
+    const uint64_t dims[3] = {128, static_cast<uint64_t>(p.num_kv_heads), big};
+    const uint64_t ks[2] = {static_cast<uint64_t>(p.k_stride_head) * 2, static_cast<uint64_t>(p.k_stride_tok) * 2};
+    const uint64_t vs[2] = {static_cast<uint64_t>(p.v_stride_head) * 2, static_cast<uint64_t>(p.v_stride_tok) * 2};
+    const uint32_t box[3] = {64, 1, BN};
+    if (!make_map(&tk, p.k, 3, dims, ks, box) || !make_map(&tv, p.v, 3, dims, vs, box)) return MSA_ERR_LAUNCH;
+  }
+  static bool attr_done[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !attr_done[dev]) {
+    if (cudaFuncSetAttribute(fmha_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return MSA_ERR_LAUNCH;
+    if (dev < 16) attr_done[dev] = true;
+  }
+  fmha_tc_kernel<<<p.num_work, NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv, g_knobs);
+  return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
+}
+
 }  // namespace msa
+
+// Debug hook while the descriptor constants are being validated on hardware.
+extern "C" void msa_debug_tc_knobs(uint32_t k_lbo, uint32_t k_sbo, uint32_t v_lbo, uint32_t v_sbo, uint32_t v_kstep,
+                                   uint32_t p_colstep) {
+  msa::tc::g_knobs = {k_lbo, k_sbo, v_lbo, v_sbo, v_kstep, p_colstep};
+}

@@ -34,7 +34,7 @@ class MsaFmhaParams(ctypes.Structure):
         ("k_stride_page", _i64), ("k_stride_head", _i64), ("k_stride_tok", _i64),
         ("v_stride_page", _i64), ("v_stride_head", _i64), ("v_stride_tok", _i64),
         ("out_stride_tok", _i64), ("out_stride_head", _i64),
-        ("kbi_stride_tok", _i64), ("kbi_stride_head", _i64),
+        ("kbi_stride_tok", _i64), ("kbi_stride_head", _i64), ("kv_extent", _i64),
         ("total_q", _i32), ("num_qo_heads", _i32), ("num_kv_heads", _i32), ("batch", _i32),
         ("num_work", _i32), ("block_m", _i32), ("pack", _i32), ("page_size", _i32),
         ("kv_block_num", _i32), ("num_splits", _i32), ("max_k_tiles", _i32),

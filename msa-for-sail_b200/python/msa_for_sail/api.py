@@ -7,6 +7,7 @@ shapes and error behaviour.  Underneath, the upstream per-variant JIT is
 replaced by one prebuilt C-ABI library of sm_100a kernels (see ``_lib``).
 """
 
+import ctypes
 import math
 from typing import Optional, Tuple, Union
 
@@ -23,6 +24,27 @@ __all__ = [
 ]
 
 KV_TILE = 128
+_USE_TC = True                          # route eligible prefill shapes to the tcgen05 kernel
+_FORCE_TC = False                       # ... even when the planner would rather split KV
+_STATUS = {}
+
+
+def _status_word(device):
+    """Per-device int32 status word the kernels report bounded-wait timeouts into."""
+    idx = torch.device(device).index or 0
+    if idx not in _STATUS:
+        _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _STATUS[idx]
+
+
+def last_status(device=None, reset=True):
+    """Read (synchronously) the device status word: 0 = ok, 1 = a kernel wait timed out."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _status_word(device)
+    v = int(w.item())
+    if reset and v:
+        w.zero_()
+    return v
 _PACK_FACTORS = (2, 4, 6, 8, 16)       # upstream jit.py _PACK_FACTORS
 _NUM_SMS = {}
 
@@ -290,7 +312,6 @@ def _fmha_sail_plan(
         cap = 1024
         spr = np.ones(max(1, total_q), np.int32)
         max_splits = _lib._i32(1)
-        import ctypes
         while True:
             host = np.empty((cap, 8), np.int32)
             n = _lib.lib.msa_plan_dense(ctypes.byref(args), host.ctypes.data, cap, spr.ctypes.data,
@@ -308,6 +329,24 @@ def _fmha_sail_plan(
         info["_work_host"] = host[:n]
         if splits > 1:
             splits_per_row = upload(spr[:total_q])
+        # second work list in 256-row items for the tcgen05 prefill kernel (bf16, unsplit, one
+        # query head per row tile, ragged K/V or 128-key pages)
+        info["work_tc"], info["num_work_tc"] = None, 0
+        info["tc_preferred"] = False
+        if pack == 1 and max_qo > 128 and not use_fp8_kvcache and page_size in (-1, 0, 128):
+            args_tc = _lib.MsaPlanArgs(
+                a_q.ctypes.data, a_k.ctypes.data, a_o.ctypes.data, batch, num_qo_heads, hkv, 256, 1,
+                1, num_sms, 0)
+            cap_tc = max(16, (total_q // 256 + batch) * num_qo_heads)
+            host_tc = np.empty((cap_tc, 8), np.int32)
+            n_tc = _lib.check(_lib.lib.msa_plan_dense(ctypes.byref(args_tc), host_tc.ctypes.data, cap_tc,
+                                                      None, None), "msa_plan_dense")
+            if n_tc:
+                wt = arena.take(n_tc * 8, torch.int32)
+                wt.copy_(torch.from_numpy(host_tc[:n_tc].reshape(-1)))
+                info["work_tc"], info["num_work_tc"] = wt, n_tc
+                # with too few items to fill the GPU the split-KV plan of the generic kernel wins
+                info["tc_preferred"] = splits == 1 or n_tc >= num_sms
 
     if splits > 1:
         info["workspace_o"] = arena.take(splits * total_q * orig_num_qo_heads * 128, torch.float32)
@@ -596,7 +635,10 @@ def _fmha_sail(
     p.kv_len = plan["kv_segment_lens"].data_ptr()
     p.qo_offset = qo_offset.data_ptr()
     splits = plan["num_kv_splits"]
-    use_split = output_o and splits > 1
+    use_tc = (plan.get("work_tc") is not None and output_o and kv_block_indexes is None
+              and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+              and page_size in (0, 128) and _USE_TC and (plan["tc_preferred"] or _FORCE_TC))
+    use_split = output_o and splits > 1 and not use_tc
     if out is not None:
         p.out = out.data_ptr()
         p.out_stride_tok, p.out_stride_head = out.stride(0), out.stride(1)
@@ -632,13 +674,16 @@ def _fmha_sail(
     p.k_scale_head, p.v_scale_head = _ptr(k_head), _ptr(v_head)
     p.total_q, p.num_qo_heads, p.num_kv_heads, p.batch = nnz_qo, num_qo_heads, num_kv_heads, batch
     p.block_m, p.pack = plan["qo_tile_size"], plan["pack_factor"]
+    p.kv_extent = k.shape[0]
+    if use_tc:
+        p.work, p.num_work, p.block_m = plan["work_tc"].data_ptr(), plan["num_work_tc"], 256
+    p.status = _status_word(q.device).data_ptr()
     p.q_dtype, p.kv_dtype = _dt_code(q.dtype), _dt_code(k.dtype)
     p.flags = (FLAG_OUT_O if output_o else 0) | (FLAG_OUT_SCORE if max_score is not None else 0) | \
               (FLAG_SPARSE if kv_block_indexes is not None else 0)
     p.sm_scale = float(q_s * k_s * sm_scale)
     p.out_scale = float(v_s * o_s)
 
-    import ctypes
     stream = _stream()
     _lib.check(_lib.lib.msa_fmha_fwd(ctypes.byref(p), stream), "msa_fmha_fwd")
 
