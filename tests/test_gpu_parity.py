@@ -27,6 +27,25 @@ def _i32(x):
     return torch.tensor(x, dtype=torch.int32)
 
 
+@pytest.fixture(params=["tcgen05", "mma"])
+def kernel_path(request):
+    """Run a dense test twice: with the tcgen05 prefill kernel wherever the shape is eligible
+    (forced even when the planner would rather split KV), and on the generic mma.sync kernel."""
+    from msa_for_sail import api
+    old = (api._USE_TC, api._FORCE_TC)
+    api._USE_TC = api._FORCE_TC = request.param == "tcgen05"
+    yield request.param
+    api._USE_TC, api._FORCE_TC = old
+
+
+@pytest.fixture(autouse=True)
+def _no_kernel_timeouts():
+    yield
+    from msa_for_sail import api
+    torch.cuda.synchronize()
+    assert api.last_status() == 0, "a kernel reported a bounded-wait timeout"
+
+
 # ---------------------------------------------------------------------------
 # top-k
 # ---------------------------------------------------------------------------
@@ -127,7 +146,7 @@ def test_lse_merge_matches_oracle():
 # ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("name", ["prefill", "chunked", "decode", "offset"])
-def test_dense_golden(name):
+def test_dense_golden(name, kernel_path):
     api = _api()
     z = load_golden(f"attn_{name}.npz")
     b, ql, kl, hq, hk, off = [int(x) for x in z["meta"]]
@@ -148,8 +167,10 @@ def test_dense_golden(name):
     ([3, 2, 4], [260, 128, 131], 8, 2, -1),          # short chunks, packed rows > 16
     ([0, 5, 3], [64, 0, 70], 4, 2, 1),               # empty q, empty kv
     ([300], [300], 2, 1, 3),                         # prefill with forced splits
+    ([1000, 257, 640], [1000, 1300, 640], 8, 2, 1),  # multi-tile prefill, tails, chunked prefill
+    ([2048], [2048], 2, 2, 1),
 ])
-def test_dense_ragged_matches_oracle(qo_lens, kv_lens, hq, hk, splits):
+def test_dense_ragged_matches_oracle(qo_lens, kv_lens, hq, hk, splits, kernel_path):
     api = _api()
     g = gen(sum(qo_lens) + sum(kv_lens) + hq)
     q = randn_bf16(g, sum(qo_lens), hq, 128)
@@ -172,8 +193,10 @@ def test_dense_ragged_matches_oracle(qo_lens, kv_lens, hq, hk, splits):
     (16, False, [90, 33], [100, 333], 4, 2, 1),
     (64, True, [1, 1, 1], [640, 100, 1], 8, 2, -1),
     (128, False, [1, 1, 1, 1], [2048, 1500, 128, 129], 16, 2, 4),
+    (128, False, [700, 1500], [1211, 1500], 4, 2, 1),        # prefill over shuffled pages, tail page
+    (128, True, [513], [2000], 4, 1, 1),
 ])
-def test_dense_paged_matches_oracle(page_size, nhd, qo_lens, kv_lens, hq, hk, splits):
+def test_dense_paged_matches_oracle(page_size, nhd, qo_lens, kv_lens, hq, hk, splits, kernel_path):
     api = _api()
     g = gen(page_size + sum(kv_lens))
     q = randn_bf16(g, sum(qo_lens), hq, 128)
@@ -190,7 +213,7 @@ def test_dense_paged_matches_oracle(page_size, nhd, qo_lens, kv_lens, hq, hk, sp
     check_out(out, ref, "paged")
 
 
-def test_offset_override_and_noncausal():
+def test_offset_override_and_noncausal(kernel_path):
     api = _api()
     g = gen(21)
     qo_lens, kv_lens, hq, hk = [50, 20], [300, 280], 4, 2
@@ -212,7 +235,7 @@ def test_offset_override_and_noncausal():
     check_out(out, orc.attention(q, k, v, qo_lens, kv_lens, hq, hk, qo_offset=off), "nc+override")
 
 
-def test_mixed_prefill_decode_split():
+def test_mixed_prefill_decode_split(kernel_path):
     api = _api()
     g = gen(31)
     qo_lens, kv_lens, hq, hk = [1, 2, 300, 200], [500, 64, 300, 777], 8, 2
@@ -256,7 +279,7 @@ def test_maxscore_golden():
     (True, [1, 1], [700, 256], 4, 4, True, torch.float32),
     (False, [140], [600], 2, 2, False, torch.bfloat16),
 ])
-def test_maxscore_matches_oracle(paged, qo_lens, kv_lens, hq, hk, full, ms_dtype):
+def test_maxscore_matches_oracle(paged, qo_lens, kv_lens, hq, hk, full, ms_dtype, kernel_path):
     api = _api()
     g = gen(sum(kv_lens) + hq * 7)
     q = randn_bf16(g, sum(qo_lens), hq, 128)
