@@ -153,6 +153,26 @@ int msa_plan_dense(const MsaPlanArgs* args, MsaWorkItem* work, int32_t capacity,
                    int32_t* splits_per_row /* [total_q] host */,
                    int32_t* max_splits_out);
 
+/* Split-KV forward + merge with the partial-result scratch held inside the library.
+ * No counterpart in the upstream project (there the caller always owns the split
+ * workspace, api.py:141-167).  It exists for embedders that may not allocate device
+ * memory at call time -- an engine whose memory pool owns the whole device after
+ * start-up, a sandboxed plugin host that passes tensors but no allocator.  Same
+ * arguments as msa_fmha_fwd (dense or sparse, MSA_FLAG_OUT_O only, block_m 16/64/128)
+ * with partial_o / partial_lse left NULL and num_splits = the S of the work list;
+ * the result goes to params->out (and params->lse).  The call performs no
+ * cudaMalloc / cudaFree and calls no allocating routine.
+ *  - Limit: num_splits * total_q * num_qo_heads <= MSA_STATIC_SCRATCH_MAX_ROWS,
+ *    otherwise MSA_ERR_TOO_LARGE.  The array (about 8.5 MB) is resident on every GPU
+ *    that loads the library, until the process exits.
+ *  - The first call on a device resolves the array's device address; make that first
+ *    call before any stream capture on that device.
+ *  - All calls on a device share the one array: two calls whose kernels overlap on the
+ *    GPU (different streams) race on it.  Serialise them on one stream. */
+#define MSA_STATIC_SCRATCH_MAX_ROWS 16384
+int msa_fmha_fwd_split_static(const MsaFmhaParams* params, const int32_t* splits_per_row,
+                              msa_stream_t stream);
+
 /* Human-readable text of an MSA_ERR_* code. */
 const char* msa_status_string(int code);
 

@@ -51,7 +51,7 @@ class MsaPlanArgs(ctypes.Structure):
 
 #: every symbol include/msa_b200.h declares
 EXPORTS = ("msa_fmha_fwd", "msa_lse_merge", "msa_topk_select", "msa_plan_dense",
-           "msa_status_string", "msa_build_arch", "msa_sizeof")
+           "msa_status_string", "msa_build_arch", "msa_sizeof", "msa_fmha_fwd_split_static")
 
 
 def _load():
@@ -81,6 +81,8 @@ def _load():
     lib.msa_status_string.argtypes = [ctypes.c_int]
     lib.msa_status_string.restype = ctypes.c_char_p
     lib.msa_build_arch.restype = ctypes.c_int
+    lib.msa_fmha_fwd_split_static.argtypes = [ctypes.POINTER(MsaFmhaParams), _p, _p]
+    lib.msa_fmha_fwd_split_static.restype = ctypes.c_int
     return lib
 
 
