@@ -41,7 +41,7 @@ def attention_flops(batch, q_len, kv_len, h_q, causal=True):
 WORKLOADS = {
     # name: (batch, q_len, kv_len, h_q, h_kv)
     "paged_prefill_b4_s8192_h64kv8": (4, 8192, 8192, 64, 8),
-    "paged_prefill_b1_s2048_h16kv2": (1, 2048, 2048, 16, 2),      # small case for ncu captures
+    "paged_prefill_b2_s4096_h32kv4": (2, 4096, 4096, 32, 4),      # small case for ncu captures (150 MB)
 }
 DEFAULT = "paged_prefill_b4_s8192_h64kv8"
 

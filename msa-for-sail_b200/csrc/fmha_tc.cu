@@ -8,13 +8,15 @@
 // "B" that walk the same KV tiles, so every K/V tile in shared memory feeds two MMAs and the
 // softmax of one Q tile overlaps the tensor-core work of the other.
 //
-//   warp 0      TMA producer: Q once, then K and V tiles (2-deep rings each) by
+//   warps 0-3   softmax of tile A: thread r owns row r (TMEM lane r): one TMEM read of the S
+//   warps 4-7   softmax of tile B  row, mask, row max, optional max-score store, exp2, bf16 P
+//               written back over S, lazy rescale of O, final normalise + store
+//   warp 8      TMA producer: Q once, then K and V tiles (2-deep rings each) by
 //               cp.async.bulk.tensor with the physical page as a run-time coordinate
-//   warp 1      MMA issuer (one elected lane): S = Q K^T into TMEM, O += P V with P read from
+//   warp 9      MMA issuer (one elected lane): S = Q K^T into TMEM, O += P V with P read from
 //               TMEM; completion is signalled to mbarriers with tcgen05.commit
-//   warps 2-5   softmax of tile A: thread r owns row r (TMEM lane r): mask, row max, optional
-//   warps 6-9   softmax of tile B  max-score store, exp2, bf16 P written back over S, lazy
-//               rescale of O, final normalise + store
+//   warps 10-11 idle (they complete the third warpgroup so that setmaxnreg can move their
+//               registers to the softmax warpgroups: 224 / 224 / 56 per thread)
 //
 // TMEM (512 columns): S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P aliases the
 // first 64 columns of its S.  Shared memory: Q 64 KB, K 2x32 KB, V 2x32 KB, all in the
@@ -40,14 +42,18 @@ constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
 constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
 constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // + alignment slack
-constexpr int NTHREADS = 320;
+constexpr int NTHREADS = 384;
+constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
 constexpr float kRescaleThreshold = 8.0f;          // log2 units: P stays <= 2^8
+constexpr uint32_t kEmuMask = 0x5252;              // pairs (of 16 per 32 columns) whose exp2 is computed on the FMA pipe
 
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13,
            V_FIX = 15, NUM_BARS = 16 };
 
-struct Knobs {            // descriptor constants (bytes)
+struct Knobs {            // descriptor constants (bytes) + optional per-phase clock trace
   uint32_t k_lbo, k_sbo, v_lbo, v_sbo, v_kstep, p_colstep;
+  unsigned long long* trace;   // [4 roles][512 tiles][8 tags] clock64 samples of one CTA, or null
+  int trace_cta;
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -63,6 +69,10 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool tracing = kn.trace != nullptr && static_cast<int>(blockIdx.x) == kn.trace_cta;
+  auto trace = [&](int role, int j, int tag) {
+    if (tracing && j < 512) kn.trace[(role * 512 + j) * 8 + tag] = clock64();
+  };
 
   // ---------------- work item ----------------
   const MsaWorkItem w = p.work[blockIdx.x];
@@ -98,7 +108,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -107,10 +117,11 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == PRODUCER_WARP) {
     // =========================== TMA producer ===========================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_arrive_expect_tx(bar(Q_FULL), 2 * TILE_BYTES);
 #pragma unroll
       for (int x = 0; x < 2; ++x)
@@ -119,6 +130,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
           tma_load_3d(smem_base + OFF_Q + x * TILE_BYTES + hlf * SUB_BYTES, &tm_q, bar(Q_FULL), hlf * 64, head,
                       qo_base + row0 + x * BM);
     }
+    __syncwarp();
     const int page_base = paged ? p.kv_page_indptr[b] : 0;
     const int kv_base = paged ? 0 : p.kv_start[b];
     uint32_t fix_phase = 0;
@@ -128,30 +140,34 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       const int page = paged ? p.kv_indices[page_base + j] : 0;
       const int valid_rows = min(BN, kv_len - j * BN);
       const bool fix = valid_rows < BN;                 // tail tile: rows past kv_len must read as 0 in V
-      if (lane == 0) {
-        alive = mbar_wait(bar(K_EMPTY + ks), ((j / KSTAGES) & 1) ^ 1, abort_flag);
-        if (alive) {
-          mbar_arrive_expect_tx(bar(K_FULL + ks), TILE_BYTES);
+      if (lane == 0) trace(3, j, 0);
+      alive = mbar_wait(bar(K_EMPTY + ks), ((j / KSTAGES) & 1) ^ 1, abort_flag);
+      if (lane == 0) trace(3, j, 1);
+      if (!alive) break;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(bar(K_FULL + ks), TILE_BYTES);
 #pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf) {
-            const uint32_t dst = smem_base + OFF_K + ks * TILE_BYTES + hlf * SUB_BYTES;
-            if (paged) tma_load_4d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, 0, kvh, page);
-            else tma_load_3d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, kvh, kv_base + j * BN);
-          }
-          alive = mbar_wait(bar(V_EMPTY + vs), ((j / VSTAGES) & 1) ^ 1, abort_flag);
-        }
-        if (alive) {
-          const uint32_t vbar = fix ? bar(V_FIX) : bar(V_FULL + vs);
-          mbar_arrive_expect_tx(vbar, TILE_BYTES);
-#pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf) {
-            const uint32_t dst = smem_base + OFF_V + vs * TILE_BYTES + hlf * SUB_BYTES;
-            if (paged) tma_load_4d(dst, &tm_v, vbar, hlf * 64, 0, kvh, page);
-            else tma_load_3d(dst, &tm_v, vbar, hlf * 64, kvh, kv_base + j * BN);
-          }
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          const uint32_t dst = smem_base + OFF_K + ks * TILE_BYTES + hlf * SUB_BYTES;
+          if (paged) tma_load_4d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, 0, kvh, page);
+          else tma_load_3d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, kvh, kv_base + j * BN);
         }
       }
-      alive = __shfl_sync(0xffffffffu, alive, 0);
+      __syncwarp();
+      alive = mbar_wait(bar(V_EMPTY + vs), ((j / VSTAGES) & 1) ^ 1, abort_flag);
+      if (lane == 0) trace(3, j, 2);
+      if (!alive) break;
+      if (elect_one()) {
+        const uint32_t vbar = fix ? bar(V_FIX) : bar(V_FULL + vs);
+        mbar_arrive_expect_tx(vbar, TILE_BYTES);
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          const uint32_t dst = smem_base + OFF_V + vs * TILE_BYTES + hlf * SUB_BYTES;
+          if (paged) tma_load_4d(dst, &tm_v, vbar, hlf * 64, 0, kvh, page);
+          else tma_load_3d(dst, &tm_v, vbar, hlf * 64, kvh, kv_base + j * BN);
+        }
+      }
+      __syncwarp();
       if (fix && alive) {
         alive = mbar_wait(bar(V_FIX), fix_phase, abort_flag);
         alive = __all_sync(0xffffffffu, alive);
@@ -169,67 +185,87 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == MMA_WARP) {
     // =========================== MMA issuer ===========================
-    if (lane == 0) {
-      constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false, false);
-      constexpr uint32_t IDESC_PV = idesc_bf16(BM, kHeadDim, false, true);
-      bool alive = n_total > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag) : true;
-      auto issue_qk = [&](int x, int j) {
-        const int ks = j % KSTAGES;
-        const uint32_t qa = smem_base + OFF_Q + x * TILE_BYTES, ka = smem_base + OFF_K + ks * TILE_BYTES;
+    // The whole warp walks the loop (waits are warp-uniform); the tcgen05 instructions are
+    // issued by the one lane elect.sync picks, so their operands can live in uniform registers.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false, false);
+    constexpr uint32_t IDESC_PV = idesc_bf16(BM, kHeadDim, false, true);
+    // descriptor templates: K-major operands (Q, K): LBO unused (16 B), SBO 1024 B;
+    // MN-major V: LBO 16384 B (next 64 columns), SBO 1024 B (next 8 keys)
+    const uint64_t dk_hi = smem_desc(0, 16, 1024) & 0xFFFFFFFFFFFF0000ull;
+    const uint64_t dv_hi = smem_desc(0, 2 * SUB_BYTES / 2, 1024) & 0xFFFFFFFFFFFF0000ull;
+    auto issue_qk = [&](int x, int j) {
+      const uint32_t qa = (smem_base + OFF_Q + x * TILE_BYTES) >> 4;
+      const uint32_t ka = (smem_base + OFF_K + (j % KSTAGES) * TILE_BYTES) >> 4;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t o = (k >> 2) * SUB_BYTES + (k & 3) * 32;
-          mma_ss(tmem + x * BN, smem_desc(qa + o, kn.k_lbo, kn.k_sbo), smem_desc(ka + o, kn.k_lbo, kn.k_sbo),
-                 IDESC_QK, k > 0);
-        }
-      };
-      auto issue_pv = [&](int x, int j) {
-        const int vs = j % VSTAGES;
-        const uint32_t va = smem_base + OFF_V + vs * TILE_BYTES;
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t o = ((k >> 2) * SUB_BYTES + (k & 3) * 32) >> 4;
+        mma_ss(tmem + x * BN, dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+      }
+    };
+    auto issue_pv = [&](int x, int j) {
+      const uint32_t va = (smem_base + OFF_V + (j % VSTAGES) * TILE_BYTES) >> 4;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_ts(tmem + 256 + x * kHeadDim, tmem + x * BN + k * kn.p_colstep,
-                 smem_desc(va + k * kn.v_kstep, kn.v_lbo, kn.v_sbo), IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
-      };
-      if (alive && n_total > 0) {
-        alive = mbar_wait(bar(K_FULL + 0), 0, abort_flag);
-        if (alive) {
-          tc_fence_after();
+      for (int k = 0; k < 8; ++k)
+        mma_ts(tmem + 256 + x * kHeadDim, tmem + x * BN + k * 8, dv_hi | ((va + k * (2048 >> 4)) & 0x3FFF), IDESC_PV,
+               (j > 0 || k > 0) ? 1u : 0u);
+    };
+    bool alive = n_total > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag) : true;
+    if (alive && n_total > 0) {
+      alive = mbar_wait(bar(K_FULL + 0), 0, abort_flag);
+      if (alive) {
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
           for (int x = 0; x < 2; ++x)
             if (n_tiles[x] > 0) { issue_qk(x, 0); mma_commit(bar(S_FULL + x)); }
           mma_commit(bar(K_EMPTY + 0));
         }
+        __syncwarp();
       }
-      for (int j = 0; j < n_total && alive; ++j) {
+    }
+    for (int j = 0; j < n_total && alive; ++j) {
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          if (j >= n_tiles[x] || !alive) continue;
-          alive = mbar_wait(bar(P_FULL + x), j & 1, abort_flag);
-          if (alive) alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag);
-          if (!alive) break;
-          tc_fence_after();
-          issue_pv(x, j);
-          if (j + 1 < n_tiles[x]) {
+      for (int x = 0; x < 2; ++x) {
+        if (j >= n_tiles[x] || !alive) continue;
+        if (lane == 0) trace(2, j, x * 4 + 0);
+        const bool more = j + 1 < n_tiles[x];
+        // the tiles this step reads normally landed long ago: check them before P, and only once per j
+        if (x == 0 || j >= n_tiles[0]) {
+          alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag);
+          if (alive && j + 1 < n_total)
             alive = mbar_wait(bar(K_FULL + (j + 1) % KSTAGES), ((j + 1) / KSTAGES) & 1, abort_flag);
-            if (!alive) break;
-            tc_fence_after();
+        }
+        if (lane == 0) trace(2, j, x * 4 + 1);
+        if (alive) alive = mbar_wait(bar(P_FULL + x), j & 1, abort_flag);
+        if (!alive) break;
+        tc_fence_after();
+        if (lane == 0) trace(2, j, x * 4 + 2);
+        if (elect_one()) {
+          issue_pv(x, j);
+          if (more) {
             issue_qk(x, j + 1);
             mma_commit(bar(S_FULL + x));
           } else {
             mma_commit(bar(O_FULL + x));
           }
+          if (x == 1 || j >= n_tiles[1]) {          // last user of this V stage / next K stage
+            mma_commit(bar(V_EMPTY + j % VSTAGES));
+            if (j + 1 < n_total) mma_commit(bar(K_EMPTY + (j + 1) % KSTAGES));
+          }
         }
-        if (!alive) break;
-        mma_commit(bar(V_EMPTY + j % VSTAGES));
-        if (j + 1 < n_total) mma_commit(bar(K_EMPTY + (j + 1) % KSTAGES));
+        __syncwarp();
+        if (lane == 0) trace(2, j, x * 4 + 3);
       }
     }
+  } else if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   } else {
     // =========================== softmax / epilogue ===========================
-    const int x = (warp - 2) >> 2;                       // 0: tile A, 1: tile B
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int x = warp >> 2;                             // 0: tile A, 1: tile B
     const int r = ((warp & 3) << 5) | lane;              // row in tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
     const uint32_t tS = tmem + x * BN + lane_addr;
@@ -246,27 +282,35 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     bool alive = true;
 
     for (int j = 0; j < nx && alive; ++j) {
+      if (r == 0) trace(x, j, 0);
       alive = mbar_wait(bar(S_FULL + x), j & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
+      if (r == 0) trace(x, j, 1);
       const int pos0 = j * BN;
       const bool need_mask = (pos0 + BN - 1 > m0 + off) || (pos0 + BN > kv_len);
-      // ---- pass 1: row max of the raw scores ----
-      float mx = -INFINITY;
+      // ---- one read of the whole S row (128 fp32) ----
+      uint32_t sv[4][32];
+      tmem_ld32(tS, sv[0]);
+      tmem_ld32(tS + 32, sv[1]);
+      tmem_ld32(tS + 64, sv[2]);
+      tmem_ld32(tS + 96, sv[3]);
+      tmem_wait_ld();
+      if (r == 0) trace(x, j, 2);
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_wait_ld();
-        if (need_mask) {
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            if (pos0 + c * 32 + e <= lim) mx = fmaxf(mx, __uint_as_float(v[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-        }
+            if (pos0 + c * 32 + e > lim) sv[c][e] = 0xff800000u;     // -inf
       }
+      float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four independent chains
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int e = 0; e < 32; e += 2)
+          mxs[(e >> 1) & 3] = max3(mxs[(e >> 1) & 3], __uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1]));
+      const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       if (want_score && row_ok && j < p.max_k_tiles) {
         const int64_t o = (static_cast<int64_t>(head) * p.max_k_tiles + j) * p.total_q + gtok;
         if (p.max_score_dtype == MSA_DT_BF16) static_cast<__nv_bfloat16*>(p.max_score)[o] = __float2bfloat16_rn(mx);
@@ -289,29 +333,59 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         }
       }
       const float msafe = (m_used == -INFINITY) ? 0.f : m_used;
-      // ---- pass 2: P = exp2(S * scale - m), bf16, written over the first half of S ----
+      if (r == 0) trace(x, j, 3);
+      // ---- P = exp2(S * scale - m) as bf16, written over the first half of S ----
+      // The special-function unit does 16 exp2 per clock per SM, a quarter of what the tensor
+      // pipe needs here, so kEmuMask selects pairs whose exp2 runs on the FMA pipe instead:
+      // round-to-nearest split x = n + f, degree-3 polynomial for 2^f (rel. error 7.5e-5, far
+      // below the bf16 rounding of P), n added into the exponent field.  All fp32 arithmetic
+      // is done on packed pairs (fma.rn.f32x2 / add.rn.f32x2).
+      const uint64_t scale2 = f2_pack(scale_log2, scale_log2);
+      const uint64_t negm2 = f2_pack(-msafe, -msafe);
+      uint64_t lsum2 = f2_pack(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = exp2_fast(fmaf(__uint_as_float(v[e]), scale_log2, -msafe));
-          float p1 = exp2_fast(fmaf(__uint_as_float(v[e + 1]), scale_log2, -msafe));
-          if (need_mask) {
-            if (pos0 + c * 32 + e > lim) p0 = 0.f;
-            if (pos0 + c * 32 + e + 1 > lim) p1 = 0.f;
+          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])), scale2, negm2);
+          float p0, p1;
+          if ((kEmuMask >> ((e >> 1) & 15)) & 1) {
+            float x0, x1;
+            f2_unpack(x2, x0, x1);
+            const uint64_t xc = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));     // also maps -inf
+            const uint64_t t2 = f2_add(xc, f2_pack(12582912.f, 12582912.f));          // 1.5 * 2^23: n in the low bits
+            const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
+            const uint64_t fr = f2_fma(n2, f2_pack(-1.f, -1.f), xc);                   // f in [-0.5, 0.5]
+            uint64_t pl = f2_fma(fr, f2_pack(0.055171650f, 0.055171650f), f2_pack(0.24261113f, 0.24261113f));
+            pl = f2_fma(pl, fr, f2_pack(0.69326097f, 0.69326097f));
+            pl = f2_fma(pl, fr, f2_pack(0.99992806f, 0.99992806f));
+            float q0, q1, t0, t1;
+            f2_unpack(pl, q0, q1);
+            f2_unpack(t2, t0, t1);
+            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+          } else {
+            float x0, x1;
+            f2_unpack(x2, x0, x1);
+            p0 = exp2_fast(x0);
+            p1 = exp2_fast(x1);
           }
-          l_sum += p0 + p1;
+          lsum2 = f2_add(lsum2, f2_pack(p0, p1));
           pk[e >> 1] = pack2<false>(p0, p1);
         }
         tmem_st16(tS + c * 16, pk);
       }
+      {
+        float l0, l1;
+        f2_unpack(lsum2, l0, l1);
+        l_sum += l0 + l1;
+      }
+      if (r == 0) trace(x, j, 4);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(P_FULL + x));
+      if (r == 0) trace(x, j, 5);
     }
 
     // ---- epilogue ----
@@ -355,7 +429,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0 && p.status) atomicExch(p.status, MSA_STATUS_TIMEOUT);
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -392,7 +466,7 @@ bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-Knobs g_knobs = {16, 1024, 16384, 1024, 2048, 8};
+Knobs g_knobs = {16, 1024, 16384, 1024, 2048, 8, nullptr, 0};
 
 }  // namespace
 
@@ -453,5 +527,10 @@ int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 // Debug hook while the descriptor constants are being validated on hardware.
 extern "C" void msa_debug_tc_knobs(uint32_t k_lbo, uint32_t k_sbo, uint32_t v_lbo, uint32_t v_sbo, uint32_t v_kstep,
                                    uint32_t p_colstep) {
-  msa::tc::g_knobs = {k_lbo, k_sbo, v_lbo, v_sbo, v_kstep, p_colstep};
+  msa::tc::g_knobs.k_lbo = k_lbo; msa::tc::g_knobs.k_sbo = k_sbo; msa::tc::g_knobs.v_lbo = v_lbo;
+  msa::tc::g_knobs.v_sbo = v_sbo; msa::tc::g_knobs.v_kstep = v_kstep; msa::tc::g_knobs.p_colstep = p_colstep;
+}
+extern "C" void msa_debug_tc_trace(unsigned long long* buf, int cta) {
+  msa::tc::g_knobs.trace = buf;
+  msa::tc::g_knobs.trace_cta = cta;
 }
