@@ -84,6 +84,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   const int kv_len = p.kv_len[b];
   const int off = p.qo_offset[b];
   const bool paged = p.page_size > 0;
+  const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;     // false: score-only pass, no V, no P, no O
   int n_tiles[2];
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
@@ -154,6 +155,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         }
       }
       __syncwarp();
+      if (!has_o) continue;
       alive = mbar_wait(bar(V_EMPTY + vs), ((j / VSTAGES) & 1) ^ 1, abort_flag);
       if (lane == 0) trace(3, j, 2);
       if (!alive) break;
@@ -168,7 +170,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         }
       }
       __syncwarp();
-      if (fix && alive) {
+      if (fix && alive && has_o) {
         alive = mbar_wait(bar(V_FIX), fix_phase, abort_flag);
         alive = __all_sync(0xffffffffu, alive);
         fix_phase ^= 1;
@@ -234,7 +236,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         const bool more = j + 1 < n_tiles[x];
         // the tiles this step reads normally landed long ago: check them before P, and only once per j
         if (x == 0 || j >= n_tiles[0]) {
-          alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag);
+          if (has_o) alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag);
           if (alive && j + 1 < n_total)
             alive = mbar_wait(bar(K_FULL + (j + 1) % KSTAGES), ((j + 1) / KSTAGES) & 1, abort_flag);
         }
@@ -244,15 +246,15 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         tc_fence_after();
         if (lane == 0) trace(2, j, x * 4 + 2);
         if (elect_one()) {
-          issue_pv(x, j);
+          if (has_o) issue_pv(x, j);
           if (more) {
             issue_qk(x, j + 1);
             mma_commit(bar(S_FULL + x));
-          } else {
+          } else if (has_o) {
             mma_commit(bar(O_FULL + x));
           }
           if (x == 1 || j >= n_tiles[1]) {          // last user of this V stage / next K stage
-            mma_commit(bar(V_EMPTY + j % VSTAGES));
+            if (has_o) mma_commit(bar(V_EMPTY + j % VSTAGES));
             if (j + 1 < n_total) mma_commit(bar(K_EMPTY + (j + 1) % KSTAGES));
           }
         }
@@ -315,6 +317,11 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         const int64_t o = (static_cast<int64_t>(head) * p.max_k_tiles + j) * p.total_q + gtok;
         if (p.max_score_dtype == MSA_DT_BF16) static_cast<__nv_bfloat16*>(p.max_score)[o] = __float2bfloat16_rn(mx);
         else static_cast<float*>(p.max_score)[o] = mx;
+      }
+      if (!has_o) {                    // score-only pass: S is consumed, hand the buffer back
+        tc_fence_before();
+        mbar_arrive(bar(P_FULL + x));
+        continue;
       }
       // ---- running max with lazy rescale ----
       const float m_cand = fmaxf(m_used, mx * scale_log2);
@@ -389,8 +396,8 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     }
 
     // ---- epilogue ----
-    if (alive && nx > 0) alive = mbar_wait(bar(O_FULL + x), 0, abort_flag);
-    if (alive) {
+    if (alive && nx > 0 && has_o) alive = mbar_wait(bar(O_FULL + x), 0, abort_flag);
+    if (alive && has_o) {
       tc_fence_after();
       const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
       const float inv = l_sum > 0.f ? p.out_scale * vsh / l_sum : 0.f;
@@ -481,9 +488,10 @@ int fmha_tc_supported(const MsaFmhaParams& p) {
 int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   using namespace tc;
   if (p.q_dtype != MSA_DT_BF16 || p.kv_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
-  if ((p.flags & MSA_FLAG_SPARSE) || !(p.flags & MSA_FLAG_OUT_O) || p.partial_o || p.pack != 1) return MSA_ERR_UNSUPPORTED;
+  if ((p.flags & MSA_FLAG_SPARSE) || p.partial_o || p.pack != 1) return MSA_ERR_UNSUPPORTED;
   if (p.page_size != 0 && p.page_size != BN) return MSA_ERR_UNSUPPORTED;
-  if (!p.out || !p.v) return MSA_ERR_BAD_ARG;
+  const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;
+  if (has_o && (!p.out || !p.v)) return MSA_ERR_BAD_ARG;
   if (p.num_work <= 0) return MSA_OK;
 
   CUtensorMap tq, tk, tv;
@@ -502,13 +510,13 @@ int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
     const uint64_t vs[3] = {static_cast<uint64_t>(p.v_stride_tok) * 2, static_cast<uint64_t>(p.v_stride_head) * 2,
                             static_cast<uint64_t>(p.v_stride_page) * 2};
     const uint32_t box[4] = {64, BN, 1, 1};
-    if (!make_map(&tk, p.k, 4, dims, ks, box) || !make_map(&tv, p.v, 4, dims, vs, box)) return MSA_ERR_LAUNCH;
+    if (!make_map(&tk, p.k, 4, dims, ks, box) || !make_map(&tv, has_o ? p.v : p.k, 4, dims, has_o ? vs : ks, box)) return MSA_ERR_LAUNCH;
   } else {
     const uint64_t dims[3] = {128, static_cast<uint64_t>(p.num_kv_heads), big};
     const uint64_t ks[2] = {static_cast<uint64_t>(p.k_stride_head) * 2, static_cast<uint64_t>(p.k_stride_tok) * 2};
     const uint64_t vs[2] = {static_cast<uint64_t>(p.v_stride_head) * 2, static_cast<uint64_t>(p.v_stride_tok) * 2};
     const uint32_t box[3] = {64, 1, BN};
-    if (!make_map(&tk, p.k, 3, dims, ks, box) || !make_map(&tv, p.v, 3, dims, vs, box)) return MSA_ERR_LAUNCH;
+    if (!make_map(&tk, p.k, 3, dims, ks, box) || !make_map(&tv, has_o ? p.v : p.k, 3, dims, has_o ? vs : ks, box)) return MSA_ERR_LAUNCH;
   }
   static bool attr_done[16] = {};
   int dev = 0;

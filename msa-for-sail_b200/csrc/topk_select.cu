@@ -9,8 +9,10 @@
 //
 // Layout of the work: a CTA owns 32 consecutive tokens of one head; its lanes read 32
 // consecutive tokens (one coalesced 128-byte line per page row for fp32), its SL warps scan
-// interleaved page slices, each thread keeping TOPK 64-bit keys (ord << 32 | ~page) in
-// registers with min-replacement.  The SL partial lists are merged through shared memory.
+// interleaved blocks of TOPK pages.  Each thread keeps its TOPK best 64-bit keys
+// (ord << 32 | ~page) sorted in registers and folds in TOPK new keys at a time with bitonic
+// compare-exchange networks (branch-free: rows of a warp never diverge).  The SL partial lists
+// are merged through shared memory with the same network.
 // HBM traffic is one read of the valid part of the score tensor plus the index write; no
 // transpose workspace (upstream needs one, api.py:1818-1821).
 #include "common.cuh"
@@ -25,26 +27,50 @@ __device__ __forceinline__ uint32_t ord_key(float v) {
   return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
 }
 
+using u64 = unsigned long long;
+
+__device__ __forceinline__ void ce_desc(u64& a, u64& b) {      // a >= b afterwards
+  const u64 hi = a > b ? a : b, lo = a > b ? b : a;
+  a = hi; b = lo;
+}
+
+// Sorted (descending) list of the TOPK best keys seen so far, updated TOPK keys at a time with
+// fixed compare-exchange networks: no data-dependent branch, so the 32 rows a warp owns never
+// diverge.  Keys are unique (page index in the low word), hence no tie handling.
 template <int TOPK>
 struct TopList {
-  unsigned long long key[TOPK];
-  unsigned long long min_key;
-  int min_slot;
+  u64 key[TOPK];
   __device__ __forceinline__ void init() {
 #pragma unroll
-    for (int i = 0; i < TOPK; ++i) key[i] = 0ull;   // below every real key (ord >= 1 for real scores, and ~page != 0)
-    min_key = 0ull; min_slot = 0;
+    for (int i = 0; i < TOPK; ++i) key[i] = 0ull;               // below every real key
   }
-  __device__ __forceinline__ void find_min() {
-    min_key = key[0]; min_slot = 0;
+  // bitonic sort of a block, descending
+  static __device__ __forceinline__ void sort_desc(u64 (&v)[TOPK]) {
 #pragma unroll
-    for (int i = 1; i < TOPK; ++i) if (key[i] < min_key) { min_key = key[i]; min_slot = i; }
+    for (int k = 2; k <= TOPK; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+        for (int i = 0; i < TOPK; ++i) {
+          const int l = i ^ j;
+          if (l > i) {
+            if ((i & k) == 0) ce_desc(v[i], v[l]); else ce_desc(v[l], v[i]);
+          }
+        }
+      }
+    }
   }
-  __device__ __forceinline__ void offer(unsigned long long k) {
-    if (k > min_key) {
+  // merge another descending list: keep the TOPK largest of the 2*TOPK keys, sorted
+  __device__ __forceinline__ void merge_sorted(const u64 (&v)[TOPK]) {
 #pragma unroll
-      for (int i = 0; i < TOPK; ++i) if (i == min_slot) key[i] = k;
-      find_min();
+    for (int i = 0; i < TOPK; ++i) key[i] = key[i] > v[TOPK - 1 - i] ? key[i] : v[TOPK - 1 - i];   // bitonic now
+#pragma unroll
+    for (int j = TOPK >> 1; j > 0; j >>= 1) {
+#pragma unroll
+      for (int i = 0; i < TOPK; ++i) {
+        const int l = i ^ j;
+        if (l > i) ce_desc(key[i], key[l]);
+      }
     }
   }
 };
@@ -53,7 +79,7 @@ template <int TOPK, typename T>
 __global__ void __launch_bounds__(256)
 topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles,
                    int total_q, int nvp, int force_begin, int force_end_start, int slices) {
-  extern __shared__ unsigned long long s_keys[];   // [slices][32][TOPK]
+  extern __shared__ u64 s_keys[];   // [slices][32][TOPK]
   const int lane = threadIdx.x & 31, sl = threadIdx.x >> 5;
   const int tok_blocks = (total_q + 31) / 32;
   const int head = blockIdx.x / tok_blocks;
@@ -64,39 +90,36 @@ topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
   top.init();
   if (live) {
     const T* base = scores + static_cast<size_t>(head) * max_k_tiles * total_q + t;
-    constexpr int UNROLL = 8;
-    int k = sl;
-    const int step = slices;
-    // pages scanned by this slice: sl, sl + slices, ...
-    for (; k + (UNROLL - 1) * step < nvp; k += UNROLL * step) {
-      float v[UNROLL];
+    // slice sl scans page blocks sl, sl + slices, ... of TOPK consecutive pages each
+    for (int k0 = sl * TOPK; k0 < nvp; k0 += slices * TOPK) {
+      float v[TOPK];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = static_cast<float>(base[static_cast<size_t>(k + u * step) * total_q]);
+      for (int u = 0; u < TOPK; ++u)
+        v[u] = (k0 + u < nvp) ? static_cast<float>(base[static_cast<size_t>(k0 + u) * total_q]) : 0.f;
+      u64 blk[TOPK];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int kk = k + u * step;
+      for (int u = 0; u < TOPK; ++u) {
+        const int kk = k0 + u;
         const bool forced = kk < force_begin || kk >= force_end_start;
         const uint32_t o = forced ? kForcedOrd : ord_key(v[u]);
-        top.offer((static_cast<unsigned long long>(o) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(kk)));
+        blk[u] = kk < nvp ? ((static_cast<u64>(o) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(kk))) : 0ull;
       }
-    }
-    for (; k < nvp; k += step) {
-      const float v = static_cast<float>(base[static_cast<size_t>(k) * total_q]);
-      const bool forced = k < force_begin || k >= force_end_start;
-      const uint32_t o = forced ? kForcedOrd : ord_key(v);
-      top.offer((static_cast<unsigned long long>(o) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(k)));
+      TopList<TOPK>::sort_desc(blk);
+      top.merge_sorted(blk);
     }
   }
   if (slices > 1) {
-    unsigned long long* mine = s_keys + (static_cast<size_t>(sl) * 32 + lane) * TOPK;
+    u64* mine = s_keys + (static_cast<size_t>(sl) * 32 + lane) * TOPK;
 #pragma unroll
     for (int i = 0; i < TOPK; ++i) mine[i] = top.key[i];
     __syncthreads();
     if (sl != 0) return;
     for (int s2 = 1; s2 < slices; ++s2) {
-      const unsigned long long* other = s_keys + (static_cast<size_t>(s2) * 32 + lane) * TOPK;
+      const u64* other = s_keys + (static_cast<size_t>(s2) * 32 + lane) * TOPK;
+      u64 o[TOPK];
 #pragma unroll
-      for (int i = 0; i < TOPK; ++i) top.offer(other[i]);
+      for (int i = 0; i < TOPK; ++i) o[i] = other[i];
+      top.merge_sorted(o);
     }
   }
   if (!live) return;
@@ -105,13 +128,21 @@ topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
   uint32_t idx[TOPK];
 #pragma unroll
   for (int i = 0; i < TOPK; ++i) idx[i] = top.key[i] == 0ull ? 0xffffffffu : ~static_cast<uint32_t>(top.key[i]);
-  // ascending odd-even transposition sort (fully unrolled, static register indices)
+  // ascending bitonic sort of the indices (static register indices)
 #pragma unroll
-  for (int pass = 0; pass < TOPK; ++pass) {
+  for (int k = 2; k <= TOPK; k <<= 1) {
 #pragma unroll
-    for (int i = (pass & 1); i + 1 < TOPK; i += 2) {
-      const uint32_t a = idx[i], b = idx[i + 1];
-      idx[i] = min(a, b); idx[i + 1] = max(a, b);
+    for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+      for (int i = 0; i < TOPK; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const uint32_t a = idx[i], b = idx[l];
+          const bool up = (i & k) == 0;
+          idx[i] = up ? min(a, b) : max(a, b);
+          idx[l] = up ? max(a, b) : min(a, b);
+        }
+      }
     }
   }
   int32_t* dst = out + (static_cast<size_t>(t) * num_heads + head) * TOPK;
@@ -146,7 +177,7 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
   const long long ctas = static_cast<long long>(tok_blocks) * H;
   // enough slices to put ~16 warps on every SM, bounded by the pages there are to scan
   int slices = 1;
-  while (slices < 8 && ctas * slices < 148LL * 16 && nvp / (slices * 2) >= TOPK) slices *= 2;
+  while (slices < 8 && ctas * slices < 148LL * 16 && nvp / (slices * 2) >= 2 * TOPK) slices *= 2;
   if (ctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   const size_t smem = slices > 1 ? static_cast<size_t>(slices) * 32 * TOPK * sizeof(unsigned long long) : 0;
   auto kern = topk_select_kernel<TOPK, T>;

@@ -635,7 +635,7 @@ def _fmha_sail(
     p.kv_len = plan["kv_segment_lens"].data_ptr()
     p.qo_offset = qo_offset.data_ptr()
     splits = plan["num_kv_splits"]
-    use_tc = (plan.get("work_tc") is not None and output_o and kv_block_indexes is None
+    use_tc = (plan.get("work_tc") is not None and kv_block_indexes is None
               and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
               and page_size in (0, 128) and _USE_TC and (plan["tc_preferred"] or _FORCE_TC))
     use_split = output_o and splits > 1 and not use_tc
