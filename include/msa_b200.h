@@ -80,6 +80,10 @@ typedef struct MsaFmhaParams {
   const float*   k_scale_head;     /* optional [Hkv] de-quantisation scale of K             */
   const float*   v_scale_head;     /* optional [Hkv] de-quantisation scale of V             */
   int32_t*       status;           /* optional device status word                            */
+  const int32_t* page_batch;       /* optional [num_logical_pages] batch item owning each entry of kv_indices */
+  void*          sparse_ws;        /* optional workspace of msa_sparse_workspace_bytes() bytes: enables the
+                                      page-major (KV-outer) sparse prefill path                             */
+  int64_t        sparse_ws_bytes;
   int64_t q_stride_tok, q_stride_head;
   int64_t k_stride_page, k_stride_head, k_stride_tok;   /* ragged: page stride unused       */
   int64_t v_stride_page, v_stride_head, v_stride_tok;
@@ -94,6 +98,7 @@ typedef struct MsaFmhaParams {
   int32_t kv_block_num;    /* sparse: entries per (token, kv head)                           */
   int32_t num_splits;      /* size of the S dimension of the partial workspace (1 = unsplit) */
   int32_t max_k_tiles;     /* second dimension of max_score                                  */
+  int32_t num_logical_pages; /* length of kv_indices (sparse page-major path)                        */
   int32_t q_dtype, kv_dtype, max_score_dtype;
   int32_t flags;           /* MSA_FLAG_*                                                     */
   float   sm_scale;        /* q_scale * k_scale * softmax scale                              */
@@ -107,12 +112,19 @@ typedef struct MsaFmhaParams {
  * and the caller runs msa_lse_merge afterwards. */
 int msa_fmha_fwd(const MsaFmhaParams* params, msa_stream_t stream);
 
+/* Bytes of MsaFmhaParams.sparse_ws needed by the page-major sparse prefill path (reverse
+ * index page -> tokens, per-slot partial O in bf16 and LSE).  No upstream counterpart: there
+ * sparse attention always runs token by token (csrc/include/prepare_plan_metadata.cuh:90-112). */
+int64_t msa_sparse_workspace_bytes(int64_t total_q, int32_t num_qo_heads, int32_t num_kv_heads,
+                                   int32_t kv_block_num, int64_t num_logical_pages);
+
 /* Split-KV merge: out[t,h,:] = sum_s w_s * partial_o[s,t,h,:] / sum_s w_s with
  * w_s = exp(partial_lse[s,t,h] - max_s); a -inf LSE gives weight 0 and its
  * partial is ignored.  splits_per_row ([total_q] or NULL = num_splits for all)
  * bounds s per token.  Replaces `reduction` (csrc/fmha_sm80_reduction.cu:42-104,
  * csrc/include/sm80_fmha_reduction.hpp:74-216). */
-int msa_lse_merge(const float* partial_o, const float* partial_lse,
+int msa_lse_merge(const void* partial_o, int32_t partial_dtype /* MSA_DT_F32 | MSA_DT_BF16 */,
+                  const float* partial_lse,
                   const int32_t* splits_per_row, void* out, float* lse_out,
                   int32_t num_splits, int32_t total_q, int32_t num_heads,
                   int64_t out_stride_tok, int64_t out_stride_head,

@@ -8,6 +8,9 @@ namespace msa {
 int fmha_mma_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_tc_supported(const MsaFmhaParams& p);
 int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
+int fmha_sparse_tc_supported(const MsaFmhaParams& p);
+int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
+int64_t fmha_sparse_tc_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
 }  // namespace msa
 
 extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
@@ -48,6 +51,7 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
   if (p.out && ((p.out_stride_tok * 2) % 16 || (p.out_stride_head * 2) % 16)) return MSA_ERR_BAD_ARG;
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (msa::fmha_sparse_tc_supported(p)) return msa::fmha_sparse_tc_launch(p, stream);
   if (msa::fmha_tc_supported(p)) return msa::fmha_tc_launch(p, stream);
   return msa::fmha_mma_launch(p, stream);
 }
@@ -121,6 +125,14 @@ extern "C" int msa_plan_dense(const MsaPlanArgs* a, MsaWorkItem* work, int32_t c
   if (static_cast<long long>(items.size()) > capacity) return MSA_ERR_TOO_LARGE;
   std::copy(items.begin(), items.end(), work);
   return static_cast<int>(items.size());
+}
+
+extern "C" int64_t msa_sparse_workspace_bytes(int64_t total_q, int32_t num_qo_heads, int32_t num_kv_heads,
+                                              int32_t kv_block_num, int64_t num_logical_pages) {
+  if (total_q < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads || kv_block_num <= 0 ||
+      num_logical_pages < 0)
+    return MSA_ERR_BAD_ARG;
+  return msa::fmha_sparse_tc_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages);
 }
 
 extern "C" const char* msa_status_string(int code) {

@@ -479,6 +479,12 @@ Knobs g_knobs = {16, 1024, 16384, 1024, 2048, 8, nullptr, 0};
 
 }  // namespace tc
 
+// bf16 tensor map with a 128-byte swizzle (shared with the sparse page-major kernel)
+int make_tma_map_bf16(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box) {
+  return tc::make_map(m, base, rank, dims, strides_bytes, box) ? MSA_OK : MSA_ERR_LAUNCH;
+}
+
 // Shapes the tcgen05 kernel takes; everything else runs on the mma.sync kernel.
 int fmha_tc_supported(const MsaFmhaParams& p) {
   if (p.block_m != 256) return 0;

@@ -4,15 +4,16 @@
 //
 // A split whose LSE is -inf contributes nothing and its partial is never multiplied in (it may
 // hold NaN or stale bytes).  Same contract as the upstream reduction
-// (csrc/include/sm80_fmha_reduction.hpp:133-215); partials here are fp32 and the LSE is a
-// natural logarithm.  One warp handles one (token, head): lane l owns columns 4l..4l+3.
+// (csrc/include/sm80_fmha_reduction.hpp:133-215); partials here are fp32 or bf16 and the LSE
+// is a natural logarithm.  One warp handles one (token, head): lane l owns columns 4l..4l+3.
 #include "common.cuh"
 
 namespace msa {
 namespace {
 
+template <bool PBF16>
 __global__ void __launch_bounds__(256)
-lse_merge_kernel(const float* __restrict__ po, const float* __restrict__ pl, const int32_t* __restrict__ spr,
+lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, const int32_t* __restrict__ spr,
                  __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int num_splits, int total_q,
                  int num_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale) {
   const int lane = threadIdx.x & 31;
@@ -32,7 +33,16 @@ lse_merge_kernel(const float* __restrict__ po, const float* __restrict__ pl, con
   float sw = 0.f;
   for (int s = 0; s < S; ++s) {
     const float l = pl[static_cast<int64_t>(s) * rows + row];
-    const float4 v = *reinterpret_cast<const float4*>(po + (static_cast<int64_t>(s) * rows + row) * kHeadDim + lane * 4);
+    float4 v;
+    if constexpr (PBF16) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(po_) +
+                                                        (static_cast<int64_t>(s) * rows + row) * kHeadDim + lane * 4);
+      v = make_float4(bf16_bits_to_float(raw.x & 0xffff), bf16_bits_to_float(raw.x >> 16),
+                      bf16_bits_to_float(raw.y & 0xffff), bf16_bits_to_float(raw.y >> 16));
+    } else {
+      v = *reinterpret_cast<const float4*>(static_cast<const float*>(po_) +
+                                           (static_cast<int64_t>(s) * rows + row) * kHeadDim + lane * 4);
+    }
     if (l != -INFINITY) {                      // value select after an unconditional load
       const float w = __expf(l - mxs);
       sw += w;
@@ -54,18 +64,24 @@ lse_merge_kernel(const float* __restrict__ po, const float* __restrict__ pl, con
 }  // namespace
 }  // namespace msa
 
-extern "C" int msa_lse_merge(const float* partial_o, const float* partial_lse, const int32_t* splits_per_row,
-                             void* out, float* lse_out, int32_t num_splits, int32_t total_q, int32_t num_heads,
-                             int64_t out_stride_tok, int64_t out_stride_head, float out_scale,
-                             msa_stream_t stream) {
+extern "C" int msa_lse_merge(const void* partial_o, int32_t partial_dtype, const float* partial_lse,
+                             const int32_t* splits_per_row, void* out, float* lse_out, int32_t num_splits,
+                             int32_t total_q, int32_t num_heads, int64_t out_stride_tok, int64_t out_stride_head,
+                             float out_scale, msa_stream_t stream) {
   if (!partial_o || !partial_lse || (!out && !lse_out) || num_splits < 1 || total_q < 0 || num_heads <= 0)
     return MSA_ERR_BAD_ARG;
   const int64_t rows = static_cast<int64_t>(total_q) * num_heads;
   if (rows == 0) return MSA_OK;
   const int64_t blocks = (rows + 7) / 8;
   if (blocks > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
-  msa::lse_merge_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      partial_o, partial_lse, splits_per_row, static_cast<__nv_bfloat16*>(out), lse_out, num_splits, total_q,
-      num_heads, out_stride_tok, out_stride_head, out_scale);
+  if (partial_dtype != MSA_DT_F32 && partial_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
+  if (partial_dtype == MSA_DT_BF16)
+    msa::lse_merge_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        partial_o, partial_lse, splits_per_row, static_cast<__nv_bfloat16*>(out), lse_out, num_splits, total_q,
+        num_heads, out_stride_tok, out_stride_head, out_scale);
+  else
+    msa::lse_merge_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        partial_o, partial_lse, splits_per_row, static_cast<__nv_bfloat16*>(out), lse_out, num_splits, total_q,
+        num_heads, out_stride_tok, out_stride_head, out_scale);
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
 }

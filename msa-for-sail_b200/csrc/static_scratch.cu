@@ -67,6 +67,6 @@ extern "C" int msa_fmha_fwd_split_static(const MsaFmhaParams* pp, const int32_t*
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int rc = fmha_mma_launch(p, stream);
   if (rc != MSA_OK) return rc;
-  return msa_lse_merge(p.partial_o, p.partial_lse, splits_per_row, p.out, user_lse, p.num_splits, p.total_q,
+  return msa_lse_merge(p.partial_o, MSA_DT_F32, p.partial_lse, splits_per_row, p.out, user_lse, p.num_splits, p.total_q,
                        p.num_qo_heads, p.out_stride_tok, p.out_stride_head, p.out_scale, stream_);
 }

@@ -30,6 +30,7 @@ class MsaFmhaParams(ctypes.Structure):
         ("qo_start", _p), ("kv_start", _p), ("kv_len", _p), ("qo_offset", _p),
         ("kv_page_indptr", _p), ("kv_indices", _p), ("kv_block_indexes", _p), ("token_batch", _p),
         ("work", _p), ("k_scale_head", _p), ("v_scale_head", _p), ("status", _p),
+        ("page_batch", _p), ("sparse_ws", _p), ("sparse_ws_bytes", _i64),
         ("q_stride_tok", _i64), ("q_stride_head", _i64),
         ("k_stride_page", _i64), ("k_stride_head", _i64), ("k_stride_tok", _i64),
         ("v_stride_page", _i64), ("v_stride_head", _i64), ("v_stride_tok", _i64),
@@ -37,7 +38,7 @@ class MsaFmhaParams(ctypes.Structure):
         ("kbi_stride_tok", _i64), ("kbi_stride_head", _i64), ("kv_extent", _i64),
         ("total_q", _i32), ("num_qo_heads", _i32), ("num_kv_heads", _i32), ("batch", _i32),
         ("num_work", _i32), ("block_m", _i32), ("pack", _i32), ("page_size", _i32),
-        ("kv_block_num", _i32), ("num_splits", _i32), ("max_k_tiles", _i32),
+        ("kv_block_num", _i32), ("num_splits", _i32), ("max_k_tiles", _i32), ("num_logical_pages", _i32),
         ("q_dtype", _i32), ("kv_dtype", _i32), ("max_score_dtype", _i32), ("flags", _i32),
         ("sm_scale", _f32), ("out_scale", _f32),
     ]
@@ -51,7 +52,8 @@ class MsaPlanArgs(ctypes.Structure):
 
 #: every symbol include/msa_b200.h declares
 EXPORTS = ("msa_fmha_fwd", "msa_lse_merge", "msa_topk_select", "msa_plan_dense",
-           "msa_status_string", "msa_build_arch", "msa_sizeof", "msa_fmha_fwd_split_static")
+           "msa_status_string", "msa_build_arch", "msa_sizeof", "msa_fmha_fwd_split_static",
+           "msa_sparse_workspace_bytes")
 
 
 def _load():
@@ -72,7 +74,7 @@ def _load():
                 f"binding {ctypes.sizeof(st)} bytes; rebuild the library")
     lib.msa_fmha_fwd.argtypes = [ctypes.POINTER(MsaFmhaParams), _p]
     lib.msa_fmha_fwd.restype = ctypes.c_int
-    lib.msa_lse_merge.argtypes = [_p, _p, _p, _p, _p, _i32, _i32, _i32, _i64, _i64, _f32, _p]
+    lib.msa_lse_merge.argtypes = [_p, _i32, _p, _p, _p, _p, _i32, _i32, _i32, _i64, _i64, _f32, _p]
     lib.msa_lse_merge.restype = ctypes.c_int
     lib.msa_topk_select.argtypes = [_p, _i32, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _p]
     lib.msa_topk_select.restype = ctypes.c_int
@@ -81,6 +83,8 @@ def _load():
     lib.msa_status_string.argtypes = [ctypes.c_int]
     lib.msa_status_string.restype = ctypes.c_char_p
     lib.msa_build_arch.restype = ctypes.c_int
+    lib.msa_sparse_workspace_bytes.argtypes = [_i64, _i32, _i32, _i32, _i64]
+    lib.msa_sparse_workspace_bytes.restype = _i64
     lib.msa_fmha_fwd_split_static.argtypes = [ctypes.POINTER(MsaFmhaParams), _p, _p]
     lib.msa_fmha_fwd_split_static.restype = ctypes.c_int
     return lib

@@ -26,6 +26,8 @@ __all__ = [
 KV_TILE = 128
 _USE_TC = True                          # route eligible prefill shapes to the tcgen05 kernel
 _FORCE_TC = False                       # ... even when the planner would rather split KV
+_USE_SPARSE_TC = True                   # page-major (KV-outer) tcgen05 path for sparse prefill
+_FORCE_SPARSE_TC = False                # ... even when few tokens share a page
 _STATUS = {}
 
 
@@ -303,6 +305,13 @@ def _fmha_sail_plan(
             while splits * 2 <= min(kv_block_num, 8) and items * splits < 2 * num_sms:
                 splits *= 2
         info["token_batch"] = upload(np.repeat(np.arange(batch, dtype=np.int32), qo_lens))
+        pages_per = [(kl + page_size - 1) // page_size for kl in kv_lens]
+        info["page_batch"] = upload(np.repeat(np.arange(batch, dtype=np.int32), pages_per))
+        info["num_logical_pages"] = int(sum(pages_per))
+        info["sparse_ws"] = None
+        # page-major path pays off once several tokens share a page
+        info["sparse_tc_preferred"] = (sum(pages_per) > 0 and total_q * kv_block_num >= 8 * sum(pages_per)
+                                       and total_q >= 256)
     else:
         info["token_batch"] = None
         a_q = np.asarray(qo_lens, np.int32); a_k = np.asarray(kv_lens, np.int32); a_o = np.asarray(offs, np.int32)
@@ -668,6 +677,23 @@ def _fmha_sail(
         p.kbi_stride_tok, p.kbi_stride_head = kv_block_indexes.stride(0), kv_block_indexes.stride(1)
         p.kv_block_num = kv_block_indexes.shape[2]
         p.token_batch = plan["token_batch"].data_ptr()
+        g = num_qo_heads // num_kv_heads
+        if (_USE_SPARSE_TC and (plan["sparse_tc_preferred"] or _FORCE_SPARSE_TC) and q.dtype == torch.bfloat16
+                and k.dtype == torch.bfloat16 and page_size == 128 and 128 % g == 0 and p.kv_block_num <= 32
+                and plan["num_logical_pages"] > 0):
+            need = _lib.lib.msa_sparse_workspace_bytes(nnz_qo, num_qo_heads, num_kv_heads, p.kv_block_num,
+                                                       plan["num_logical_pages"])
+            ws = plan.get("sparse_ws")
+            if ws is None or ws.numel() < need or ws.device != q.device:
+                ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+                plan["sparse_ws"] = ws
+            p.sparse_ws, p.sparse_ws_bytes = ws.data_ptr(), ws.numel()
+            p.page_batch = plan["page_batch"].data_ptr()
+            p.num_logical_pages = plan["num_logical_pages"]
+            use_split = False                     # the page-major path merges its own partials
+            p.partial_o = p.partial_lse = None
+            p.num_splits = 1
+            p.lse = _ptr(lse)
     else:
         p.work = _ptr(plan["work"])
         p.num_work = plan["num_work"]
@@ -690,7 +716,7 @@ def _fmha_sail(
     if use_split:
         spr = plan["num_kv_splits_per_row"]
         _lib.check(_lib.lib.msa_lse_merge(
-            plan["workspace_o"].data_ptr(), plan["workspace_lse"].data_ptr(), _ptr(spr),
+            plan["workspace_o"].data_ptr(), MSA_DT_F32, plan["workspace_lse"].data_ptr(), _ptr(spr),
             out.data_ptr(), _ptr(lse), splits, nnz_qo, num_qo_heads,
             out.stride(0), out.stride(1), float(v_s * o_s), stream), "msa_lse_merge")
     return out, max_score

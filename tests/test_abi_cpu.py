@@ -44,7 +44,7 @@ def test_bad_arguments_are_rejected_without_touching_the_gpu():
     p.flags = L.FLAG_OUT_O
     assert L.lib.msa_fmha_fwd(ctypes.byref(p), None) == -1          # null tensors
     assert L.lib.msa_topk_select(None, 2, None, 1, 128, 1, 16, 1, 0, 0, None) == -1
-    assert L.lib.msa_lse_merge(None, None, None, None, None, 1, 1, 1, 0, 0, 1.0, None) == -1
+    assert L.lib.msa_lse_merge(None, 2, None, None, None, None, 1, 1, 1, 0, 0, 1.0, None) == -1
     assert b"bad argument" in L.lib.msa_status_string(-1)
     with pytest.raises(RuntimeError):
         L.check(-2, "x")

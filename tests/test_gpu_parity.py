@@ -38,6 +38,17 @@ def kernel_path(request):
     api._USE_TC, api._FORCE_TC = old
 
 
+@pytest.fixture(params=["page-major", "token-major"])
+def sparse_path(request):
+    """Sparse tests run on the page-major tcgen05 path (forced even for tiny inputs) and on the
+    token-major mma.sync path."""
+    from msa_for_sail import api
+    old = (api._USE_SPARSE_TC, api._FORCE_SPARSE_TC)
+    api._USE_SPARSE_TC = api._FORCE_SPARSE_TC = request.param == "page-major"
+    yield request.param
+    api._USE_SPARSE_TC, api._FORCE_SPARSE_TC = old
+
+
 @pytest.fixture(autouse=True)
 def _no_kernel_timeouts():
     yield
@@ -130,11 +141,23 @@ def test_lse_merge_matches_oracle():
     out = torch.empty(T, H, 128, dtype=torch.bfloat16, device=DEV)
     lse = torch.empty(T, H, dtype=torch.float32, device=DEV)
     pod, pld, sprd = po.to(DEV), pl.to(DEV), spr.to(DEV)
-    rc = _lib.lib.msa_lse_merge(pod.data_ptr(), pld.data_ptr(), sprd.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                S, T, H, out.stride(0), out.stride(1), 0.5,
+    rc = _lib.lib.msa_lse_merge(pod.data_ptr(), _lib.MSA_DT_F32, pld.data_ptr(), sprd.data_ptr(), out.data_ptr(),
+                                lse.data_ptr(), S, T, H, out.stride(0), out.stride(1), 0.5,
                                 torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     check_out(out, ref_o, "merge")
+    # bf16 partials (the sparse prefill path stores them that way)
+    pob = po.to(torch.bfloat16)
+    pob[1, :, 2] = 0          # a NaN bf16 partial behind a -inf LSE must still be ignored: keep NaN there
+    pob[1, :, 2] = float("nan")
+    ref_rows = [orc.lse_merge(pob[:int(spr[t]), t:t + 1].float(), pl[:int(spr[t]), t:t + 1], out_scale=0.5)
+                for t in range(T)]
+    pobd = pob.to(DEV)
+    rc = _lib.lib.msa_lse_merge(pobd.data_ptr(), _lib.MSA_DT_BF16, pld.data_ptr(), sprd.data_ptr(), out.data_ptr(),
+                                None, S, T, H, out.stride(0), out.stride(1), 0.5,
+                                torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    check_out(out, torch.cat(ref_rows), "merge-bf16")
     l = lse.cpu()
     assert torch.equal(torch.isinf(l), torch.isinf(ref_l))
     fin = ~torch.isinf(ref_l)
@@ -308,7 +331,7 @@ def test_maxscore_matches_oracle(paged, qo_lens, kv_lens, hq, hk, full, ms_dtype
 # sparse attention
 # ---------------------------------------------------------------------------
 
-def test_sparse_golden():
+def test_sparse_golden(sparse_path):
     api = _api()
     z = load_golden("sparse_small.npz")
     hq, hk, kbn, page = [int(x) for x in z["meta"]]
@@ -334,8 +357,11 @@ def test_sparse_golden():
     ([17], [2500], 4, 4, 16, -1, False),                     # h_r = 1
     ([3, 1], [1500, 640], 64, 2, 8, -1, False),              # h_r = 32 -> 64-row tile
     ([4, 1], [900, 2048], 8, 2, 8, 2, True),                 # all-e4m3 operands
+    ([300, 77], [1500, 700], 8, 2, 8, 1, False),             # many tokens per page, tail pages
+    ([200], [1100], 16, 1, 16, 1, False),                    # h_r = 16: 8 tokens per chunk
+    ([500], [3000], 2, 2, 4, 1, False),                      # h_r = 1: 128 tokens per chunk
 ])
-def test_sparse_matches_oracle(qo_lens, kv_lens, hq, hk, kbn, splits, fp8):
+def test_sparse_matches_oracle(qo_lens, kv_lens, hq, hk, kbn, splits, fp8, sparse_path):
     api = _api()
     g = gen(sum(kv_lens) + kbn)
     q = randn_bf16(g, sum(qo_lens), hq, 128)
@@ -395,7 +421,7 @@ def test_fp8_onlyscore():
 # the whole MSA pipeline (proxy max-score -> top-k -> sparse attention)
 # ---------------------------------------------------------------------------
 
-def test_msa_pipeline_cpu_reference_config():
+def test_msa_pipeline_cpu_reference_config(sparse_path):
     """BASELINE config 1: B=1, q=kv=4096, 16 q heads / 2 kv heads, 32 pages (shuffled table),
     1-head proxy, top-8 pages per token, sparse attention.  Indices bit-exact, O in tolerance."""
     api = _api()
