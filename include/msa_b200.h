@@ -99,6 +99,8 @@ typedef struct MsaFmhaParams {
   int32_t num_splits;      /* size of the S dimension of the partial workspace (1 = unsplit) */
   int32_t max_k_tiles;     /* second dimension of max_score                                  */
   int32_t num_logical_pages; /* length of kv_indices (sparse page-major path)                        */
+  int32_t decode_rows;     /* > 0: every item has at most this many packed rows (<= 128) and may run on the
+                              tcgen05 decode kernel; 0: do not use it                                 */
   int32_t q_dtype, kv_dtype, max_score_dtype;
   int32_t flags;           /* MSA_FLAG_*                                                     */
   float   sm_scale;        /* q_scale * k_scale * softmax scale                              */

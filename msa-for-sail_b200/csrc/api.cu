@@ -8,6 +8,8 @@ namespace msa {
 int fmha_mma_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_tc_supported(const MsaFmhaParams& p);
 int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
+int fmha_decode_tc_supported(const MsaFmhaParams& p);
+int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_sparse_tc_supported(const MsaFmhaParams& p);
 int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int64_t fmha_sparse_tc_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
@@ -52,6 +54,7 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (msa::fmha_sparse_tc_supported(p)) return msa::fmha_sparse_tc_launch(p, stream);
+  if (msa::fmha_decode_tc_supported(p)) return msa::fmha_decode_tc_launch(p, stream);
   if (msa::fmha_tc_supported(p)) return msa::fmha_tc_launch(p, stream);
   return msa::fmha_mma_launch(p, stream);
 }

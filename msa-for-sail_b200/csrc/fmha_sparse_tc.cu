@@ -35,7 +35,9 @@ constexpr int TILE_BYTES = 2 * SUB_BYTES;
 constexpr int OFF_Q = 0;                        // two Q chunk buffers
 constexpr int OFF_K = 2 * TILE_BYTES;
 constexpr int OFF_V = 3 * TILE_BYTES;
-constexpr int OFF_BAR = 4 * TILE_BYTES;
+constexpr int OFF_STAGE = 4 * TILE_BYTES;       // per softmax warpgroup: 128 rows x 256 B of bf16 O
+constexpr int OFF_ROWID = OFF_STAGE + 2 * TILE_BYTES;   // per warpgroup: 128 x int64 destination rows
+constexpr int OFF_BAR = OFF_ROWID + 2 * BM * 8;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr int NTHREADS = 384;
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
@@ -44,6 +46,10 @@ constexpr uint32_t kEmuMask = 0x5252;
 
 enum Bar { K_FULL = 0, V_FULL = 1, V_FIX = 2, Q_FULL = 3, Q_EMPTY = 5, S_FULL = 7, P_FULL = 9, O_FULL = 11,
            O_FREE = 13, NUM_BARS = 15 };
+
+// optional clock trace of one CTA (debugging aid): [4 roles][512 chunks][8 tags]
+__device__ unsigned long long g_trace[4 * 512 * 8];
+__device__ int g_trace_cta = -1;
 
 struct Ws {                 // device workspace carved by carve()
   int32_t* bin_count;       // [NB + 1]
@@ -183,6 +189,10 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool tracing = static_cast<int>(blockIdx.x) == g_trace_cta;
+  auto trace = [&](int role, int c, int tag) {
+    if (tracing && c < 512) g_trace[(role * 512 + c) * 8 + tag] = clock64();
+  };
 
   // ---------------- work item ----------------
   const int4 item = items[blockIdx.x];
@@ -253,7 +263,9 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     }
     for (int c = 0; c < n_chunks && alive; ++c) {
       const int x = c & 1, u = c >> 1;
+      if (lane == 0) trace(3, c, 0);
       alive = mbar_wait(bar(Q_EMPTY + x), (u & 1) ^ 1, abort_flag);
+      if (lane == 0) trace(3, c, 1);
       if (!alive) break;
       const int e0 = item.y + c * tpc;
       const int ntok = min(tpc, item.z - e0);
@@ -293,8 +305,11 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     for (int c = 0; c <= n_chunks && alive; ++c) {
       if (c < n_chunks) {                                   // S[x] = Q_c K^T
         const int x = c & 1, u = c >> 1;
+        if (lane == 0) trace(2, c, 0);
         alive = mbar_wait(bar(O_FREE + x), (u & 1) ^ 1, abort_flag);
+        if (lane == 0) trace(2, c, 1);
         if (alive) alive = mbar_wait(bar(Q_FULL + x), u & 1, abort_flag);
+        if (lane == 0) trace(2, c, 2);
         if (!alive) break;
         tc_fence_after();
         if (elect_one()) {
@@ -307,7 +322,9 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       if (c > 0) {                                          // O[y] = P_{c-1} V
         const int y = (c - 1) & 1, u = (c - 1) >> 1;
         if (c == 1) alive = mbar_wait(bar(V_FULL), 0, abort_flag);
+        if (lane == 0) trace(2, c, 3);
         if (alive) alive = mbar_wait(bar(P_FULL + y), u & 1, abort_flag);
+        if (lane == 0) trace(2, c, 4);
         if (!alive) break;
         tc_fence_after();
         if (elect_one()) {
@@ -315,6 +332,7 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
           mma_commit(bar(O_FULL + y));
         }
         __syncwarp();
+        if (lane == 0) trace(2, c, 5);
       }
     }
   } else if (warp >= 8) {
@@ -331,16 +349,23 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     const float scale_log2 = p.sm_scale * kLog2e * (p.k_scale_head ? p.k_scale_head[kvh] : 1.f);
     const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
     bool alive = true;
+    int entry_next = (x < n_chunks && item.y + x * tpc + r / G < item.z) ? entries[item.y + x * tpc + r / G] : 0;
     for (int c = x; c < n_chunks && alive; c += 2) {
       const int u = c >> 1;
       const int e_idx = item.y + c * tpc + r / G;
       const bool row_ok = e_idx < item.z;
-      const int entry = row_ok ? entries[e_idx] : 0;
+      const int entry = entry_next;
+      {                                                       // prefetch the entry of this warpgroup's next chunk
+        const int e_nx = e_idx + 2 * tpc;
+        entry_next = (c + 2 < n_chunks && e_nx < item.z) ? entries[e_nx] : 0;
+      }
       const int tok = entry >> 5, slot = entry & 31;
       const int lim = row_ok ? min(tok - qo_base + off, kv_len - 1) : -1;
+      if (r == 0) trace(x, c, 0);
       alive = mbar_wait(bar(S_FULL + x), u & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
+      if (r == 0) trace(x, c, 1);
       uint32_t sv[4][32];
       tmem_ld32(tS, sv[0]);
       tmem_ld32(tS + 32, sv[1]);
@@ -401,34 +426,53 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(P_FULL + x));
+      if (r == 0) trace(x, c, 2);
 
       // ---- epilogue of this chunk: normalised partial O (bf16) + LSE ----
       alive = mbar_wait(bar(O_FULL + x), u & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
+      if (r == 0) trace(x, c, 3);
       const float inv = l_sum > 0.f ? vsh / l_sum : 0.f;
       const int64_t row_id = (static_cast<int64_t>(slot) * p.total_q + tok) * p.num_qo_heads + head;
-      __nv_bfloat16* dst = partial_o + row_id * kHeadDim;
+      // stage the bf16 row in shared memory (16-byte chunks XOR-swizzled by row) so that the global
+      // stores below are whole 256-byte rows instead of 16-byte pieces of 32 different rows
+      unsigned char* stage = smem_gen + OFF_STAGE + x * TILE_BYTES;
+      int64_t* rowids = reinterpret_cast<int64_t*>(smem_gen + OFF_ROWID) + x * BM;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint32_t v[32];
         tmem_ld32(tO + cc * 32, v);
         tmem_wait_ld();
-        if (row_ok) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 o4;
-            o4.x = pack2<false>(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
-            o4.y = pack2<false>(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
-            o4.z = pack2<false>(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
-            o4.w = pack2<false>(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + cc * 32 + e) = o4;
-          }
+        for (int e = 0; e < 32; e += 8) {
+          uint4 o4;
+          o4.x = pack2<false>(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
+          o4.y = pack2<false>(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+          o4.z = pack2<false>(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
+          o4.w = pack2<false>(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+          const int chunk = cc * 4 + (e >> 3);
+          *reinterpret_cast<uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4)) = o4;
         }
       }
+      rowids[r] = row_ok ? row_id : -1;
       if (row_ok) partial_lse[row_id] = l_sum > 0.f ? msafe * kLn2 + __logf(l_sum) : -INFINITY;
       tc_fence_before();
-      mbar_arrive(bar(O_FREE + x));
+      mbar_arrive(bar(O_FREE + x));                           // TMEM slot is free again
+      if (r == 0) trace(x, c, 4);
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");
+      {
+        const int w4 = warp & 3;
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int rr = w4 * 32 + it * 2 + (lane >> 4), chunk = lane & 15;
+          const int64_t rid = rowids[rr];
+          const uint4 val = *reinterpret_cast<const uint4*>(stage + rr * 256 + ((chunk ^ (rr & 15)) << 4));
+          if (rid >= 0) __stcs(reinterpret_cast<uint4*>(partial_o + rid * kHeadDim + chunk * 8), val);   // streamed: keep L2 for Q / K / V
+        }
+      }
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");
+      if (r == 0) trace(x, c, 5);
     }
   }
 
@@ -523,3 +567,11 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 }
 
 }  // namespace msa
+
+// Debug aid: choose the CTA whose phase clocks are recorded (-1 = none) / read the record back.
+extern "C" void msa_debug_sparse_trace_cta(int cta) {
+  cudaMemcpyToSymbol(msa::sparse_tc::g_trace_cta, &cta, sizeof(int));
+}
+extern "C" void msa_debug_sparse_trace_read(unsigned long long* host_buf) {
+  cudaMemcpyFromSymbol(host_buf, msa::sparse_tc::g_trace, sizeof(unsigned long long) * 4 * 512 * 8);
+}

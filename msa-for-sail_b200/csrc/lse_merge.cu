@@ -5,60 +5,81 @@
 // A split whose LSE is -inf contributes nothing and its partial is never multiplied in (it may
 // hold NaN or stale bytes).  Same contract as the upstream reduction
 // (csrc/include/sm80_fmha_reduction.hpp:133-215); partials here are fp32 or bf16 and the LSE
-// is a natural logarithm.  One warp handles one (token, head): lane l owns columns 4l..4l+3.
+// is a natural logarithm.  Half a warp handles one (token, head).
 #include "common.cuh"
 
 namespace msa {
 namespace {
 
+// Half a warp per (token, head) row: lane l of the half owns columns 8l..8l+7.  Loads of up to
+// eight splits are issued back to back before they are consumed.
 template <bool PBF16>
 __global__ void __launch_bounds__(256)
 lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, const int32_t* __restrict__ spr,
                  __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int num_splits, int total_q,
                  int num_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);   // t * H + h
+  const int l16 = threadIdx.x & 15;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4);   // t * H + h
   const int64_t rows = static_cast<int64_t>(total_q) * num_heads;
   if (row >= rows) return;
   const int t = static_cast<int>(row / num_heads), h = static_cast<int>(row % num_heads);
   const int S = spr ? min(spr[t], num_splits) : num_splits;
 
   float mx = -INFINITY;
-  for (int s = lane; s < S; s += 32) mx = fmaxf(mx, pl[static_cast<int64_t>(s) * rows + row]);
-#pragma unroll
-  for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  for (int s = 0; s < S; ++s) mx = fmaxf(mx, __ldg(pl + static_cast<int64_t>(s) * rows + row));
   const float mxs = (mx == -INFINITY) ? 0.f : mx;
 
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
   float sw = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const float l = pl[static_cast<int64_t>(s) * rows + row];
-    float4 v;
-    if constexpr (PBF16) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(po_) +
-                                                        (static_cast<int64_t>(s) * rows + row) * kHeadDim + lane * 4);
-      v = make_float4(bf16_bits_to_float(raw.x & 0xffff), bf16_bits_to_float(raw.x >> 16),
-                      bf16_bits_to_float(raw.y & 0xffff), bf16_bits_to_float(raw.y >> 16));
-    } else {
-      v = *reinterpret_cast<const float4*>(static_cast<const float*>(po_) +
-                                           (static_cast<int64_t>(s) * rows + row) * kHeadDim + lane * 4);
+  constexpr int U = 8;
+  for (int s0 = 0; s0 < S; s0 += U) {
+    float w[U];
+    uint4 raw[U][PBF16 ? 1 : 2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int s = min(s0 + u, S - 1);                         // clamped: always a readable slot
+      const int64_t base = (static_cast<int64_t>(s) * rows + row) * kHeadDim + l16 * 8;
+      if constexpr (PBF16) {
+        raw[u][0] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(po_) + base);
+      } else {
+        raw[u][0] = *reinterpret_cast<const uint4*>(static_cast<const float*>(po_) + base);
+        raw[u][1] = *reinterpret_cast<const uint4*>(static_cast<const float*>(po_) + base + 4);
+      }
+      const float l = __ldg(pl + static_cast<int64_t>(s) * rows + row);
+      w[u] = (s0 + u < S && l != -INFINITY) ? __expf(l - mxs) : 0.f;
     }
-    if (l != -INFINITY) {                      // value select after an unconditional load
-      const float w = __expf(l - mxs);
-      sw += w;
-      acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
-      acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (w[u] != 0.f) {                                        // value select after an unconditional load
+        sw += w[u];
+        if constexpr (PBF16) {
+          const uint32_t* r4 = reinterpret_cast<const uint32_t*>(&raw[u][0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            acc[2 * c] = fmaf(w[u], bf16_bits_to_float(r4[c] & 0xffff), acc[2 * c]);
+            acc[2 * c + 1] = fmaf(w[u], bf16_bits_to_float(r4[c] >> 16), acc[2 * c + 1]);
+          }
+        } else {
+          const float* f = reinterpret_cast<const float*>(&raw[u][0]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[c] = fmaf(w[u], f[c], acc[c]);
+        }
+      }
     }
   }
   const float inv = sw > 0.f ? out_scale / sw : 0.f;
   if (out) {
-    __nv_bfloat16* dst = out + static_cast<int64_t>(t) * out_stride_tok + static_cast<int64_t>(h) * out_stride_head + lane * 4;
-    uint2 pk;
-    pk.x = pack2<false>(acc.x * inv, acc.y * inv);
-    pk.y = pack2<false>(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(dst) = pk;
+    __nv_bfloat16* dst = out + static_cast<int64_t>(t) * out_stride_tok + static_cast<int64_t>(h) * out_stride_head + l16 * 8;
+    uint4 pk;
+    pk.x = pack2<false>(acc[0] * inv, acc[1] * inv);
+    pk.y = pack2<false>(acc[2] * inv, acc[3] * inv);
+    pk.z = pack2<false>(acc[4] * inv, acc[5] * inv);
+    pk.w = pack2<false>(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4*>(dst) = pk;
   }
-  if (lse_out && lane == 0) lse_out[row] = sw > 0.f ? mxs + __logf(sw) : -INFINITY;
+  if (lse_out && l16 == 0) lse_out[row] = sw > 0.f ? mxs + __logf(sw) : -INFINITY;
 }
 
 }  // namespace
@@ -72,7 +93,7 @@ extern "C" int msa_lse_merge(const void* partial_o, int32_t partial_dtype, const
     return MSA_ERR_BAD_ARG;
   const int64_t rows = static_cast<int64_t>(total_q) * num_heads;
   if (rows == 0) return MSA_OK;
-  const int64_t blocks = (rows + 7) / 8;
+  const int64_t blocks = (rows + 15) / 16;
   if (blocks > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   if (partial_dtype != MSA_DT_F32 && partial_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
   if (partial_dtype == MSA_DT_BF16)

@@ -38,7 +38,7 @@ class MsaFmhaParams(ctypes.Structure):
         ("kbi_stride_tok", _i64), ("kbi_stride_head", _i64), ("kv_extent", _i64),
         ("total_q", _i32), ("num_qo_heads", _i32), ("num_kv_heads", _i32), ("batch", _i32),
         ("num_work", _i32), ("block_m", _i32), ("pack", _i32), ("page_size", _i32),
-        ("kv_block_num", _i32), ("num_splits", _i32), ("max_k_tiles", _i32), ("num_logical_pages", _i32),
+        ("kv_block_num", _i32), ("num_splits", _i32), ("max_k_tiles", _i32), ("num_logical_pages", _i32), ("decode_rows", _i32),
         ("q_dtype", _i32), ("kv_dtype", _i32), ("max_score_dtype", _i32), ("flags", _i32),
         ("sm_scale", _f32), ("out_scale", _f32),
     ]

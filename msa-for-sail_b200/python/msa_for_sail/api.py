@@ -26,6 +26,7 @@ __all__ = [
 KV_TILE = 128
 _USE_TC = True                          # route eligible prefill shapes to the tcgen05 kernel
 _FORCE_TC = False                       # ... even when the planner would rather split KV
+_USE_DECODE_TC = True                   # tcgen05 decode kernel for short-query bf16 shapes
 _USE_SPARSE_TC = True                   # page-major (KV-outer) tcgen05 path for sparse prefill
 _FORCE_SPARSE_TC = False                # ... even when few tokens share a page
 _STATUS = {}
@@ -704,6 +705,11 @@ def _fmha_sail(
     if use_tc:
         p.work, p.num_work, p.block_m = plan["work_tc"].data_ptr(), plan["num_work_tc"], 256
     p.status = _status_word(q.device).data_ptr()
+    rows = plan["max_qo_len"] * plan["pack_factor"] if kv_block_indexes is None else plan["pack_factor"]
+    if (_USE_DECODE_TC and not use_tc and output_o and max_score is None and q.dtype == torch.bfloat16
+            and k.dtype == torch.bfloat16 and page_size == 128 and 0 < rows <= 128
+            and plan["pack_factor"] == num_qo_heads // num_kv_heads and 128 % plan["pack_factor"] == 0):
+        p.decode_rows = rows
     p.q_dtype, p.kv_dtype = _dt_code(q.dtype), _dt_code(k.dtype)
     p.flags = (FLAG_OUT_O if output_o else 0) | (FLAG_OUT_SCORE if max_score is not None else 0) | \
               (FLAG_SPARSE if kv_block_indexes is not None else 0)

@@ -33,9 +33,10 @@ def kernel_path(request):
     (forced even when the planner would rather split KV), and on the generic mma.sync kernel."""
     from msa_for_sail import api
     old = (api._USE_TC, api._FORCE_TC)
-    api._USE_TC = api._FORCE_TC = request.param == "tcgen05"
+    api._USE_TC = api._FORCE_TC = api._USE_DECODE_TC = request.param == "tcgen05"
     yield request.param
     api._USE_TC, api._FORCE_TC = old
+    api._USE_DECODE_TC = True
 
 
 @pytest.fixture(params=["page-major", "token-major"])
@@ -45,8 +46,10 @@ def sparse_path(request):
     from msa_for_sail import api
     old = (api._USE_SPARSE_TC, api._FORCE_SPARSE_TC)
     api._USE_SPARSE_TC = api._FORCE_SPARSE_TC = request.param == "page-major"
+    api._USE_DECODE_TC = request.param == "page-major"      # token-major run also covers the mma.sync decode kernel
     yield request.param
     api._USE_SPARSE_TC, api._FORCE_SPARSE_TC = old
+    api._USE_DECODE_TC = True
 
 
 @pytest.fixture(autouse=True)
