@@ -10,6 +10,11 @@ batch (the plan is built once, as the upstream API intends: "the plan ... can be
 across layers").  The metric is effective TFLOP/s: causal-discounted algorithmic FLOPs
 (upstream bench_utils.attention_tflops) per second.
 
+Other workloads (--workload): the MSA sparse prefill pipeline (config 3: proxy max-score pass +
+page top-k + sparse attention), the MSA sparse decode step over an e4m3 cache (config 4) and the
+1M-token paged decode (config 5; with --gpus N the KV range is split over the ranks and the
+partial (O, LSE) are combined by an NCCL all-gather + the merge kernel).
+
 Prints ONE JSON line (rank 0).  `--impl reference` times the CPU oracle port of the same
 path on the host cores over a bounded sample of the same workload.
 """
@@ -39,9 +44,17 @@ def attention_flops(batch, q_len, kv_len, h_q, causal=True):
 
 
 WORKLOADS = {
-    # name: (batch, q_len, kv_len, h_q, h_kv)
-    "paged_prefill_b4_s8192_h64kv8": (4, 8192, 8192, 64, 8),
-    "paged_prefill_b2_s4096_h32kv4": (2, 4096, 4096, 32, 4),      # small case for ncu captures (150 MB)
+    # kind, parameters
+    "paged_prefill_b4_s8192_h64kv8": ("prefill", dict(b=4, ql=8192, kl=8192, hq=64, hk=8)),
+    "paged_prefill_b2_s4096_h32kv4": ("prefill", dict(b=2, ql=4096, kl=4096, hq=32, hk=4)),          # small: ncu
+    "msa_prefill_b2_s32768_h64kv8_top16": ("msa_prefill", dict(b=2, t=32768, hq=64, hk=8, topk=16)),
+    "msa_prefill_b1_s8192_h32kv4_top16": ("msa_prefill", dict(b=1, t=8192, hq=32, hk=4, topk=16)),   # small: ncu
+    "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4": (
+        "msa_decode", dict(b=32, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=True)),
+    "msa_decode_bf16_b32_kv131072_h64kv8_top16_split4": (
+        "msa_decode", dict(b=32, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=False)),
+    "paged_decode_b1_kv1048576_h64kv8": ("decode", dict(b=1, kl=1048576, hq=64, hk=8)),
+    "paged_decode_b1_kv131072_h64kv8": ("decode", dict(b=1, kl=131072, hq=64, hk=8)),               # small: ncu
 }
 DEFAULT = "paged_prefill_b4_s8192_h64kv8"
 
@@ -61,7 +74,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.rows, self.proc, self.index = [], None, index
+        self.rows, self.proc, self.index, self.first = [], None, index, 0
 
     def start(self):
         try:
@@ -92,77 +105,290 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        self.rows = self.rows[getattr(self, 'first', 0):]
-        clk = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        rows = self.rows[self.first:]
+        clk = sorted(int(r[0]) for r in rows if r and r[0].isdigit())
         mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
+        reasons = sorted({names[i] for r in rows if len(r) >= 6 for i in range(4) if r[2 + i] == "Active"})
         return {"sm_mhz": clk[len(clk) // 2] if clk else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(clk)}
 
 
-def make_inputs(workload, device, seed):
-    b, ql, kl, hq, hk = WORKLOADS[workload]
-    g = torch.Generator(device="cpu").manual_seed(seed)
-    pages_per = kl // PAGE
-    pool = b * pages_per
-    q = (torch.randn(b * ql, hq, D, generator=g) * 0.5).to(torch.bfloat16)
-    k = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16)
-    v = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16)
-    table = torch.randperm(pool, generator=g).to(torch.int32)
-    return q, k, v, table
+# ----------------------------------------------------------------------------------------------
+# workloads: each builds HBM-resident inputs, returns a dict with the step closure and the
+# algorithmic work of one step
+# ----------------------------------------------------------------------------------------------
 
+def _i32(x):
+    return torch.tensor(x, dtype=torch.int32)
+
+
+def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    pool = b * (kl // PAGE)
+    q_h = (torch.randn(b * ql, hq, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    k_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    v_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    table = torch.randperm(pool, generator=g).to(torch.int32).to(dev)
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    plan = msa.fmha_sail_plan(_i32([ql] * b), _i32([kl] * b), hq, num_kv_heads=hk, page_size=PAGE)
+    out = torch.empty(b * ql, hq, D, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(b * ql, hq, dtype=torch.float32, device=dev)
+    out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def step():
+        msa.fmha_sail(q, k, v, plan, kv_indices=table, out=out, lse=lse)
+
+    def e2e_step():
+        qd = q_h.to(dev, non_blocking=True); kd = k_h.to(dev, non_blocking=True); vd = v_h.to(dev, non_blocking=True)
+        o, _ = msa.fmha_sail(qd, kd, vd, plan, kv_indices=table)
+        out_h.copy_(o, non_blocking=True)
+
+    nbytes = (q.numel() + k.numel() + v.numel() + out.numel()) * 2
+    return dict(step=step, e2e_step=e2e_step, flops=attention_flops(b, ql, kl, hq), bytes=nbytes,
+                metric="prefill_effective_tflops", unit="TFLOP/s", bound="tensor", launches=1, graph=False,
+                h2d=(q_h.numel() + k_h.numel() + v_h.numel()) * 2, d2h=out_h.numel() * 2,
+                l2="inputs larger than L2 (Q+K+V+O = %.2f GB per GPU)" % (nbytes / 1e9),
+                cfg=dict(batch_per_gpu=b, q_len=ql, kv_len=kl, num_qo_heads=hq, num_kv_heads=hk))
+
+
+def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk):
+    """Config 3: 1-head proxy max-score pass -> page top-k -> sparse attention on the selection."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    P = t // PAGE
+    q = torch.randn(b * t, hq, D, device=dev, generator=g).to(torch.bfloat16)
+    kp = (torch.randn(b * P, hk, PAGE, D, device=dev, generator=g)
+          + math.sqrt(2.0) * torch.randn(b * P, hk, 1, 1, device=dev, generator=g)).to(torch.bfloat16)
+    vp = torch.randn(b * P, hk, PAGE, D, device=dev, generator=g).to(torch.bfloat16)
+    table = torch.randperm(b * P, device=dev, generator=g).to(torch.int32)
+    qx, kx = q[:, :1].contiguous(), kp[:, :1].contiguous()
+    lens = _i32([t] * b)
+    plan1 = msa.fmha_sail_plan(lens, lens, 1, num_kv_heads=1, page_size=PAGE, output_maxscore=True)
+    plan2 = msa.fmha_sail_plan(lens, lens, hq, num_kv_heads=hk, page_size=PAGE, kv_block_num=topk)
+    ms = torch.full((1, plan1[3]["max_k_tiles"], b * t), -float("inf"), device=dev)
+    idx = torch.empty(b * t, 1, topk, dtype=torch.int32, device=dev)
+    out = torch.empty(b * t, hq, D, dtype=torch.bfloat16, device=dev)
+
+    def s_proxy():
+        msa.fmha_sail(qx, kx, kx, plan1, kv_indices=table, output_o=False, max_score=ms)
+
+    def s_topk():
+        msa.sparse_topk_select(ms, topk, num_valid_pages=P, output=idx)
+
+    def s_sparse():
+        msa.fmha_sail(q, kp, vp, plan2, kv_indices=table, kv_block_indexes=idx.expand(b * t, hk, topk), out=out)
+
+    def step():
+        s_proxy(); s_topk(); s_sparse()
+
+    pairs = t * t - t * (t - 1) // 2
+    f_proxy = b * 1 * pairs * D * 2
+    f_sparse = b * t * hq * (topk * PAGE) * (D + D) * 2          # accessed-KV FLOPs (upstream run_msa.py:159-163)
+    out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    q_h = q.cpu().pin_memory()
+
+    def e2e_step():
+        qd = q_h.to(dev, non_blocking=True)
+        msa.fmha_sail(qd[:, :1].contiguous(), kx, kx, plan1, kv_indices=table, output_o=False, max_score=ms)
+        s_topk()
+        o, _ = msa.fmha_sail(qd, kp, vp, plan2, kv_indices=table, kv_block_indexes=idx.expand(b * t, hk, topk))
+        out_h.copy_(o, non_blocking=True)
+
+    return dict(step=step, e2e_step=e2e_step, flops=f_proxy + f_sparse, bytes=None,
+                stages=dict(proxy=(s_proxy, f_proxy, "TFLOP/s"),
+                            topk=(s_topk, ms[:, :P].numel() * 4 + idx.numel() * 4, "GB/s"),
+                            sparse=(s_sparse, f_sparse, "TFLOP/s")),
+                metric="msa_prefill_effective_tflops", unit="TFLOP/s", bound="tensor", launches=9, graph=False,
+                h2d=q_h.numel() * 2, d2h=out_h.numel() * 2,
+                l2="inputs larger than L2 (Q+O = %.2f GB per GPU); the KV cache stays resident" % (
+                    2 * q.numel() * 2 / 1e9),
+                cfg=dict(batch_per_gpu=b, q_len=t, kv_len=t, num_qo_heads=hq, num_kv_heads=hk, topk=topk,
+                         proxy_heads=1))
+
+
+def setup_msa_decode(msa, dev, seed, b, kl, hq, hk, topk, splits, fp8):
+    """Config 4: proxy max-score over a 1-head proxy cache -> top-k -> sparse decode with split-KV."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    P = kl // PAGE
+    kvdt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    q = torch.randn(b, hq, D, device=dev, generator=g).to(torch.bfloat16)
+    ks = vs = None
+    kp = torch.empty(b * P, hk, PAGE, D, device=dev, dtype=kvdt)
+    vp = torch.empty(b * P, hk, PAGE, D, device=dev, dtype=kvdt)
+    if fp8:                                      # quantise with one fp32 scale per KV head (amax / 448), in slabs
+        ks = torch.full((hk,), 5.5 / 448.0, device=dev); vs = torch.full((hk,), 5.5 / 448.0, device=dev)
+    slab = 2048
+    for s0 in range(0, b * P, slab):
+        n = min(slab, b * P - s0)
+        for dst, sc in ((kp, ks), (vp, vs)):
+            x = torch.randn(n, hk, PAGE, D, device=dev, generator=g, dtype=torch.bfloat16)
+            dst[s0:s0 + n] = (x.float() / sc.view(1, hk, 1, 1)).clamp(-448, 448).to(kvdt) if fp8 else x
+    kx = torch.randn(b * P, 1, PAGE, D, device=dev, generator=g, dtype=torch.bfloat16).to(kvdt)
+    qx = q[:, :1].contiguous().to(kvdt)
+    table = torch.randperm(b * P, device=dev, generator=g).to(torch.int32)
+    ql, kls = _i32([1] * b), _i32([kl] * b)
+    plan1 = msa.fmha_sail_plan(ql, kls, 1, num_kv_heads=1, page_size=PAGE, output_maxscore=True, use_fp8_kvcache=fp8)
+    plan2 = msa.fmha_sail_plan(ql, kls, hq, num_kv_heads=hk, page_size=PAGE, kv_block_num=topk,
+                               num_kv_splits=splits, use_fp8_kvcache=fp8)
+    ms = torch.full((1, plan1[3]["max_k_tiles"], b), -float("inf"), device=dev)
+    idx = torch.empty(b, 1, topk, dtype=torch.int32, device=dev)
+    bi = torch.empty(b, hk, topk, dtype=torch.int32, device=dev)
+    out = torch.empty(b, hq, D, dtype=torch.bfloat16, device=dev)
+    kw = dict(k_scale=ks, v_scale=vs) if fp8 else {}
+
+    def s_proxy():
+        msa.fmha_sail(qx, kx, kx, plan1, kv_indices=table, output_o=False, max_score=ms)
+
+    def s_topk():
+        msa.sparse_topk_select(ms, topk, num_valid_pages=P, output=idx)
+        bi.copy_(idx.expand(b, hk, topk))
+
+    def s_sparse():
+        msa.fmha_sail(q, kp, vp, plan2, kv_indices=table, kv_block_indexes=bi, out=out, **kw)
+
+    def step():
+        s_proxy(); s_topk(); s_sparse()
+
+    e = kp.element_size()
+    by_sparse = b * hk * topk * PAGE * 2 * D * e + 2 * b * hq * D * 2     # unique pages + Q + O
+    by_proxy = kx.numel() * kx.element_size() + ms[:, :P].numel() * 4
+    q_h = q.cpu().pin_memory(); out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        q.copy_(q_h, non_blocking=True)
+        qx.copy_(q[:, :1])
+        step()
+        out_h.copy_(out, non_blocking=True)
+
+    return dict(step=step, e2e_step=e2e_step, flops=None, bytes=by_sparse + by_proxy,
+                stages=dict(proxy=(s_proxy, by_proxy, "GB/s"), topk=(s_topk, ms[:, :P].numel() * 4, "GB/s"),
+                            sparse=(s_sparse, by_sparse, "GB/s")),
+                metric="msa_decode_kv_gbps", unit="GB/s", bound="hbm", launches=7, graph=True,
+                h2d=q_h.numel() * 2, d2h=out_h.numel() * 2,
+                l2="every step streams %.0f MB (proxy cache + selected pages) of a %.1f GB cache: larger than L2" % (
+                    (by_sparse + by_proxy) / 1e6, (kp.numel() + vp.numel()) * e / 1e9),
+                cfg=dict(batch_per_gpu=b, q_len=1, kv_len=kl, num_qo_heads=hq, num_kv_heads=hk, topk=topk,
+                         num_kv_splits=splits, kv_dtype="e4m3" if fp8 else "bf16", proxy_heads=1))
+
+
+def setup_decode(msa, dev, seed, b, kl, hq, hk, rank=0, world=1):
+    """Config 5: dense paged decode; with world > 1 this rank owns a contiguous slice of the pages."""
+    from msa_for_sail import dist as mdist
+    g = torch.Generator(device=dev).manual_seed(seed)
+    p0, p1 = mdist.shard_page_range(kl // PAGE, rank, world)
+    P = p1 - p0
+    kl_local = P * PAGE
+    q = torch.randn(b, hq, D, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).to(torch.bfloat16)
+    kp = torch.randn(b * P, hk, PAGE, D, device=dev, generator=g, dtype=torch.bfloat16)
+    vp = torch.randn(b * P, hk, PAGE, D, device=dev, generator=g, dtype=torch.bfloat16)
+    table = torch.randperm(b * P, device=dev, generator=g).to(torch.int32)
+    plan = msa.fmha_sail_plan(_i32([1] * b), _i32([kl_local] * b), hq, num_kv_heads=hk, page_size=PAGE,
+                              causal=(world == 1))
+    out = torch.empty(b, hq, D, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(b, hq, dtype=torch.float32, device=dev)
+    merged = torch.empty_like(out)
+    ws = (torch.empty(world, b, hq, D, dtype=torch.float32, device=dev),
+          torch.empty(world, b, hq, dtype=torch.float32, device=dev))
+
+    def step():
+        msa.fmha_sail(q, kp, vp, plan, kv_indices=table, out=out, lse=lse)
+        if world > 1:
+            mdist.decode_allgather_merge(out, lse, out=merged, workspace=ws)
+
+    q_h = q.cpu().pin_memory(); out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        q.copy_(q_h, non_blocking=True)
+        step()
+        out_h.copy_(merged if world > 1 else out, non_blocking=True)
+
+    nbytes = (kp.numel() + vp.numel()) * 2 + 2 * q.numel() * 2
+    return dict(step=step, e2e_step=e2e_step, flops=None, bytes=nbytes,
+                metric="decode_kv_gbps", unit="GB/s", bound="hbm", launches=2 + (1 if world > 1 else 0),
+                graph=(world == 1), h2d=q_h.numel() * 2, d2h=out_h.numel() * 2,
+                l2="inputs larger than L2 (K+V = %.2f GB per GPU)" % (nbytes / 1e9),
+                cfg=dict(batch=b, q_len=1, kv_len=kl, kv_len_per_gpu=kl_local, num_qo_heads=hq, num_kv_heads=hk,
+                         num_kv_splits=plan[3]["num_kv_splits"]))
+
+
+SETUPS = {"prefill": setup_prefill, "msa_prefill": setup_msa_prefill, "msa_decode": setup_msa_decode,
+          "decode": setup_decode}
+METRICS = {"prefill": ("prefill_effective_tflops", "TFLOP/s"), "msa_prefill": ("msa_prefill_effective_tflops", "TFLOP/s"),
+           "msa_decode": ("msa_decode_kv_gbps", "GB/s"), "decode": ("decode_kv_gbps", "GB/s")}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU reference (oracle port) on a bounded sample of the same workload
+# ----------------------------------------------------------------------------------------------
 
 def cpu_reference_sample(workload, seconds_budget, threads):
-    """Time the oracle on ONE (batch item, KV-head group) unit of the workload, restricted to the
-    last `rows` query tokens so the sample stays bounded; returns TFLOP/s over that sample."""
+    """Time the oracle on one independent unit of the workload; returns (value in the workload's
+    unit, seconds per sample, description)."""
     from oracle import msa_oracle as orc
-    b, ql, kl, hq, hk = WORKLOADS[workload]
+    kind, w = WORKLOADS[workload]
     torch.set_num_threads(threads)
-    g_heads = hq // hk
-    rows = min(ql, 1024)
     gen = torch.Generator().manual_seed(0)
-    q = (torch.randn(rows, g_heads, D, generator=gen) * 0.5).to(torch.bfloat16)
-    k = (torch.randn(kl, 1, D, generator=gen) * 0.5).to(torch.bfloat16)
-    v = (torch.randn(kl, 1, D, generator=gen) * 0.5).to(torch.bfloat16)
-    off = kl - rows
-    pairs = sum(min(kl, i + off + 1) for i in range(rows))
-    flops = g_heads * pairs * (D + D) * 2
-    orc.attention_single(q, k, v, g_heads, 1, True, off)           # warm-up
+    hq, hk = w["hq"], w["hk"]
+    g_heads = hq // hk
+    if kind in ("prefill", "msa_prefill"):
+        ql = w.get("ql", w.get("t")); kl = w.get("kl", w.get("t"))
+        rows = min(ql, 1024)
+        q = (torch.randn(rows, g_heads, D, generator=gen) * 0.5).to(torch.bfloat16)
+        if kind == "prefill":
+            k = (torch.randn(kl, 1, D, generator=gen) * 0.5).to(torch.bfloat16)
+            v = (torch.randn(kl, 1, D, generator=gen) * 0.5).to(torch.bfloat16)
+            off = kl - rows
+            pairs = sum(min(kl, i + off + 1) for i in range(rows))
+            fn = lambda: orc.attention_single(q, k, v, g_heads, 1, True, off)
+            what = f"dense causal attention, last {rows} of {ql} query tokens x {g_heads} heads over {kl} keys"
+        else:
+            keys = w["topk"] * PAGE                       # the keys a token actually attends to
+            k = torch.randn(keys, 1, D, generator=gen).to(torch.bfloat16)
+            v = torch.randn(keys, 1, D, generator=gen).to(torch.bfloat16)
+            pairs = rows * keys
+            fn = lambda: orc.attention_single(q, k, v, g_heads, 1, False, 0)
+            what = (f"attention of {rows} query tokens x {g_heads} heads over {keys} selected keys "
+                    f"(one shared page list, gather not timed)")
+        work = g_heads * pairs * (D + D) * 2 / 1e12
+    else:
+        kl = w["kl"]
+        keys = w["topk"] * PAGE if kind == "msa_decode" else min(kl, 131072)
+        q = torch.randn(1, g_heads, D, generator=gen).to(torch.bfloat16)
+        k = torch.randn(keys, 1, D, generator=gen).to(torch.bfloat16)
+        v = torch.randn(keys, 1, D, generator=gen).to(torch.bfloat16)
+        fn = lambda: orc.attention_single(q, k, v, g_heads, 1, False, 0)
+        work = keys * 2 * D * 2 / 1e9                     # GB of bf16 K+V the unit reads
+        what = f"one decode token x {g_heads} heads over {keys} keys"
+    fn()
     times = []
     t_end = time.perf_counter() + seconds_budget
-    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 20):
-        t0 = time.perf_counter()
-        orc.attention_single(q, k, v, g_heads, 1, True, off)
-        times.append(time.perf_counter() - t0)
+    while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter(); fn(); times.append(time.perf_counter() - t0)
     times.sort()
     med = times[len(times) // 2]
-    sample = (f"one (batch item, KV-head group) unit, last {rows} of {ql} query tokens x {g_heads} heads "
-              f"over {kl} keys, fp32 torch on CPU, median of {len(times)}; {b * hk} such units per step")
-    return flops / med / 1e12, med, sample
+    return work / med, med, (f"one (batch item, KV-head group) unit: {what}; fp32 torch on CPU, median of "
+                             f"{len(times)}; {w['b'] * hk} such units per step")
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    wl = args.workload
-    b, ql, kl, hq, hk = WORKLOADS[wl]
+    kind, w = WORKLOADS[args.workload]
+    metric, unit = METRICS[kind]
     vals = []
     for i in range(args.warmup + args.steps):
-        tf, med, sample = cpu_reference_sample(wl, 2.0, threads)
+        v, med, sample = cpu_reference_sample(args.workload, 1.0, threads)
         if i >= args.warmup:
-            vals.append((tf, med))
-    tf = sum(v[0] for v in vals) / len(vals)
-    ms = sum(v[1] for v in vals) / len(vals) * 1e3
+            vals.append((v, med))
+    val = sum(x[0] for x in vals) / len(vals)
+    ms = sum(x[1] for x in vals) / len(vals) * 1e3
     line = {
-        "impl": "reference", "metric": "prefill_effective_tflops", "value": tf, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl, "batch": b, "q_len": ql, "kv_len": kl, "num_qo_heads": hq,
-                   "num_kv_heads": hk, "head_dim": D, "page_size": PAGE},
-        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": dict(workload=args.workload, **w),
+        "cpu_baseline": {"value": val, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -177,15 +403,16 @@ def main():
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps from a CUDA graph")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank)
         return
+    args.warmup = max(args.warmup, 3)
 
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
@@ -194,26 +421,36 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     import msa_for_sail as msa
 
-    wl = args.workload
-    b, ql, kl, hq, hk = WORKLOADS[wl]
-    q_h, k_h, v_h, table_h = make_inputs(wl, dev, seed=1000 + rank)
-    q_h, k_h, v_h = q_h.pin_memory(), k_h.pin_memory(), v_h.pin_memory()
-    q, k, v, table = q_h.to(dev), k_h.to(dev), v_h.to(dev), table_h.to(dev)
-    lens = torch.full((b,), ql, dtype=torch.int32)
-    kv_lens = torch.full((b,), kl, dtype=torch.int32)
-    plan = msa.fmha_sail_plan(lens, kv_lens, hq, num_kv_heads=hk, page_size=PAGE)
-    out = torch.empty(b * ql, hq, D, dtype=torch.bfloat16, device=dev)
-    lse = torch.empty(b * ql, hq, dtype=torch.float32, device=dev)
-    flops = attention_flops(b, ql, kl, hq)
+    kind, w = WORKLOADS[args.workload]
+    strong = kind == "decode" and world > 1            # one sequence: its KV range is split over the ranks
+    if kind == "decode":
+        wl = SETUPS[kind](msa, dev, 1000 + rank, rank=rank, world=world, **w)
+    else:
+        wl = SETUPS[kind](msa, dev, 1000 + rank, **w)
     stream = torch.cuda.current_stream()
-
-    def step():
-        msa.fmha_sail(q, k, v, plan, kv_indices=table, out=out, lse=lse)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    step = wl["step"]
+    graphed = False
+    if wl["graph"] and not args.no_graph:
+        # decode steps are a few tens of microseconds: replay them from a CUDA graph so that the
+        # host-side launch path is not what gets measured
+        try:
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                step()
+            step, graphed = gr.replay, True
+        except Exception as exc:                                   # noqa: BLE001
+            sys.stderr.write(f"graph capture failed ({exc}); timing eager launches\n")
+            torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -230,67 +467,93 @@ def main():
     clocks = sampler.stop()
     total_ms = evs[0].elapsed_time(evs[-1])
     per = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps))
-    kernel_ms = sum(per) / len(per)                     # one launch per step: step time == kernel time
+    step_ms = sum(per) / len(per)
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
-    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    work = wl["flops"] / 1e12 if wl["unit"] == "TFLOP/s" else wl["bytes"] / 1e9
+    value = world * work / (ms_per_step * 1e-3)        # strong scaling: every rank holds 1/world of the bytes
 
-    # end to end: host buffers in, host result out, through the public API
+    # per-stage device times of a pipeline workload
+    stage_report = None
+    if "stages" in wl:
+        stage_report = {}
+        for name, (fn, wk, unit) in wl["stages"].items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            n = max(5, min(args.steps, 20))
+            run = fn
+            if wl["graph"] and not args.no_graph:
+                try:
+                    gs = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gs):
+                        fn()
+                    run = gs.replay
+                except Exception:                                  # noqa: BLE001
+                    torch.cuda.synchronize()
+            st = torch.cuda.current_stream()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(n):
+                run()
+            e1.record(st)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / n
+            stage_report[name] = {"ms": ms, "value": wk / (1e12 if unit == "TFLOP/s" else 1e9) / (ms * 1e-3),
+                                  "unit": unit}
+
     e2e = None
     if not args.no_e2e:
-        out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-        n_e2e = max(2, min(args.steps, 5))
-
-        def e2e_step():
-            qd = q_h.to(dev, non_blocking=True); kd = k_h.to(dev, non_blocking=True)
-            vd = v_h.to(dev, non_blocking=True)
-            o, _ = msa.fmha_sail(qd, kd, vd, plan, kv_indices=table)
-            out_h.copy_(o, non_blocking=True)
-
-        e2e_step()
+        n_e2e = max(2, min(args.steps, 5 if kind in ("prefill", "msa_prefill") else 50))
+        wl["e2e_step"]()
         barrier()
+        st = torch.cuda.current_stream()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        e0.record(st)
         for _ in range(n_e2e):
-            e2e_step()
-        e1.record(stream)
+            wl["e2e_step"]()
+        e1.record(st)
         barrier()
         e2e_ms = e0.elapsed_time(e1) / n_e2e
         if world > 1:
             t = torch.tensor([e2e_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
-        e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": q_h.numel() * 2 + k_h.numel() * 2 + v_h.numel() * 2,
-               "d2h_bytes_per_step": out_h.numel() * 2, "ms_per_step": e2e_ms, "steps": n_e2e}
+        e2e = {"value": world * work / (e2e_ms * 1e-3), "unit": wl["unit"], "h2d_bytes_per_step": wl["h2d"],
+               "d2h_bytes_per_step": wl["d2h"], "ms_per_step": e2e_ms, "steps": n_e2e,
+               "note": "public API call with pinned host tensors copied in and the result copied out each step"
+                       + ("; the KV cache is device-resident state" if kind != "prefill" else "")}
 
     if rank == 0:
         pk = peaks()
-        peak = pk["bf16_sustained"]
-        achieved = flops / (kernel_ms * 1e-3) / 1e12
+        if wl["bound"] == "tensor":
+            peak, psrc = pk["bf16_sustained"], pk["src"] + " (sustained cuBLAS bf16: kernel timed inside a long loop)"
+        else:
+            peak, psrc = pk["hbm"], pk["src"] + " (STREAM-style copy)"
+        achieved = work / (step_ms * 1e-3)
         line = {
-            "metric": "prefill_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl, "batch_per_gpu": b, "global_batch": b * world, "q_len": ql, "kv_len": kl,
-                       "num_qo_heads": hq, "num_kv_heads": hk, "head_dim": D, "page_size": PAGE,
-                       "l2": "inputs larger than L2 (Q+K+V+O = %.2f GB per GPU)" % (
-                           (q.numel() + k.numel() + v.numel() + out.numel()) * 2 / 1e9),
-                       "sharding": "independent (batch, KV-head group) units per GPU, no collective"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None,
-                         "peak_source": pk["src"] + " (sustained cuBLAS bf16, kernel timed inside a loop)",
-                         "kernel_ms": kernel_ms},
-            "clocks": clocks, "gpu_launches": args.steps, "e2e": e2e,
+            "metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "bf16" if not w.get("fp8") else "e4m3 cache, fp16 math", "data": "synthetic",
+            "config": dict(workload=args.workload, l2=wl["l2"], cuda_graph=graphed,
+                           sharding=("KV page range split over ranks, NCCL all-gather of (O, LSE) + merge kernel"
+                                     if strong else "independent (batch, KV-head group) units per GPU, no collective"),
+                           **wl["cfg"]),
+            "roofline": {"bound": wl["bound"], "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s" if wl["bound"] == "tensor" else "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": psrc, "step_ms": step_ms},
+            "clocks": clocks, "gpu_launches": args.steps * wl["launches"], "e2e": e2e,
         }
+        if stage_report:
+            line["stages"] = stage_report
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1
-            tf, med, sample = cpu_reference_sample(wl, 12.0, threads)
-            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                                    "sample": sample}
+            v, med, sample = cpu_reference_sample(args.workload, 12.0, threads)
+            line["cpu_baseline"] = {"value": v, "unit": wl["unit"], "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
