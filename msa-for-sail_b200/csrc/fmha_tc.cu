@@ -462,13 +462,13 @@ EncodeTiledFn encode_fn() {
 
 // rank-n bf16 map with a 128-byte swizzle; dims/strides innermost first, strides in bytes for dims 1..n-1
 bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-              const uint32_t* box) {
+              const uint32_t* box, bool bytes = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gd[5]; cuuint64_t gs[4]; cuuint32_t bx[5]; cuuint32_t es[5];
   for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gd, gs, bx, es,
+  return fn(m, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gd, gs, bx, es,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -483,6 +483,12 @@ Knobs g_knobs = {16, 1024, 16384, 1024, 2048, 8, nullptr, 0};
 int make_tma_map_bf16(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                       const uint32_t* box) {
   return tc::make_map(m, base, rank, dims, strides_bytes, box) ? MSA_OK : MSA_ERR_LAUNCH;
+}
+
+// same for 1-byte elements (e4m3 caches)
+int make_tma_map_u8(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box) {
+  return tc::make_map(m, base, rank, dims, strides_bytes, box, true) ? MSA_OK : MSA_ERR_LAUNCH;
 }
 
 // Shapes the tcgen05 kernel takes; everything else runs on the mma.sync kernel.

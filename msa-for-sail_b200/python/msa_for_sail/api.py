@@ -706,8 +706,9 @@ def _fmha_sail(
         p.work, p.num_work, p.block_m = plan["work_tc"].data_ptr(), plan["num_work_tc"], 256
     p.status = _status_word(q.device).data_ptr()
     rows = plan["max_qo_len"] * plan["pack_factor"] if kv_block_indexes is None else plan["pack_factor"]
-    if (_USE_DECODE_TC and not use_tc and output_o and max_score is None and q.dtype == torch.bfloat16
-            and k.dtype == torch.bfloat16 and page_size == 128 and 0 < rows <= 128
+    dt_ok = (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16) or k.dtype == torch.float8_e4m3fn
+    if (_USE_DECODE_TC and not use_tc and output_o != (max_score is not None) and dt_ok
+            and page_size == 128 and 0 < rows <= 128
             and plan["pack_factor"] == num_qo_heads // num_kv_heads and 128 % plan["pack_factor"] == 0):
         p.decode_rows = rows
     p.q_dtype, p.kv_dtype = _dt_code(q.dtype), _dt_code(k.dtype)

@@ -420,6 +420,27 @@ def test_fp8_onlyscore():
     check_score(ms, orc.tile_max_score(qf, kf, qo_lens, kv_lens, hk, ms.shape[1]), "fp8-ms")
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_proxy_decode_scores_paged(fp8, kernel_path):
+    """Score-only pass of a decode batch over a paged 1-head proxy cache (bf16 and e4m3)."""
+    api = _api()
+    g = gen(79 + fp8)
+    qo_lens, kv_lens, hq, hk = [1, 1, 2], [1500, 128, 700], 4, 1
+    q = randn_bf16(g, sum(qo_lens), hq, 128)
+    kp, _, table = make_paged(g, kv_lens, hk, 128)
+    if fp8:
+        q8, qf = orc.quantize_e4m3(q); k8, kf = orc.quantize_e4m3(kp)
+        qd, kd = q8.to(DEV), k8.to(DEV)
+    else:
+        qf, kf, qd, kd = q, kp, q.to(DEV), kp.to(DEV)
+    k = orc.paged_to_contiguous(kf, table, kv_lens, 128)
+    plan = api.fmha_sail_plan(_i32(qo_lens), _i32(kv_lens), hq, num_kv_heads=hk, page_size=128,
+                              output_maxscore=True, use_fp8_kvcache=fp8)
+    out, ms = api.fmha_sail(qd, kd, kd, plan, kv_indices=table.to(DEV), output_o=False)
+    assert out is None
+    check_score(ms, orc.tile_max_score(qf, k, qo_lens, kv_lens, hk, ms.shape[1]), "proxy-decode-ms")
+
+
 # ---------------------------------------------------------------------------
 # the whole MSA pipeline (proxy max-score -> top-k -> sparse attention)
 # ---------------------------------------------------------------------------
