@@ -51,8 +51,8 @@ def decode_allgather_merge(out_local: torch.Tensor, lse_local: torch.Tensor, gro
         pl = torch.empty(world, T, H, dtype=torch.float32, device=out_local.device)
     else:
         po, pl = workspace
-    dist.all_gather_into_tensor(po, po_l, group=group)
-    dist.all_gather_into_tensor(pl, pl_l, group=group)
+    dist.all_gather_into_tensor(po.view(-1), po_l.view(-1), group=group)     # flat views: rank-major layout
+    dist.all_gather_into_tensor(pl.view(-1), pl_l.view(-1), group=group)
     if out is None:
         out = torch.empty(T, H, D, dtype=torch.bfloat16, device=out_local.device)
     _lib.check(_lib.lib.msa_lse_merge(
