@@ -58,6 +58,18 @@ WORKLOADS = {
 }
 DEFAULT = "paged_prefill_b4_s8192_h64kv8"
 
+# dram__bytes_read + dram__bytes_write per launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (captured on the small variant and scaled by the units processed
+# where the full workload is too large to capture with --set full)
+TRAFFIC = {
+    "paged_prefill_b4_s8192_h64kv8": (0.90e9, "scaled x8.0 from the b2_s4096_h32kv4 capture (112 MB)"),
+    "paged_prefill_b2_s4096_h32kv4": (112.1e6, "captured"),
+    "paged_decode_b1_kv1048576_h64kv8": (4.33e9, "scaled x8 from the kv131072 capture (541.6 MB)"),
+    "paged_decode_b1_kv131072_h64kv8": (541.6e6, "captured"),
+    "msa_prefill_b1_s8192_h32kv4_top16": (1.015e9, "captured (sparse_tc_kernel; merge: 1.148e9)"),
+    "msa_prefill_b2_s32768_h64kv8_top16": (16.2e9, "scaled x16 from the b1_s8192_h32kv4 capture (sparse_tc_kernel)"),
+}
+
 
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -545,7 +557,9 @@ def main():
                            **wl["cfg"]),
             "roofline": {"bound": wl["bound"], "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s" if wl["bound"] == "tensor" else "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": psrc, "step_ms": step_ms},
+                         "traffic": TRAFFIC.get(args.workload, (None, None))[0],
+                         "traffic_source": TRAFFIC.get(args.workload, (None, "not captured"))[1],
+                         "peak_source": psrc, "step_ms": step_ms},
             "clocks": clocks, "gpu_launches": args.steps * wl["launches"], "e2e": e2e,
         }
         if stage_report:
