@@ -244,7 +244,7 @@ def setup_msa_decode(msa, dev, seed, b, kl, hq, hk, topk, splits, fp8):
                                num_kv_splits=splits, use_fp8_kvcache=fp8)
     ms = torch.full((1, plan1[3]["max_k_tiles"], b), -float("inf"), device=dev)
     idx = torch.empty(b, 1, topk, dtype=torch.int32, device=dev)
-    bi = torch.empty(b, hk, topk, dtype=torch.int32, device=dev)
+    bi = idx.expand(b, hk, topk)                 # every KV head uses the proxy head's pages: stride-0 view
     out = torch.empty(b, hq, D, dtype=torch.bfloat16, device=dev)
     kw = dict(k_scale=ks, v_scale=vs) if fp8 else {}
 
@@ -253,7 +253,6 @@ def setup_msa_decode(msa, dev, seed, b, kl, hq, hk, topk, splits, fp8):
 
     def s_topk():
         msa.sparse_topk_select(ms, topk, num_valid_pages=P, output=idx)
-        bi.copy_(idx.expand(b, hk, topk))
 
     def s_sparse():
         msa.fmha_sail(q, kp, vp, plan2, kv_indices=table, kv_block_indexes=bi, out=out, **kw)
@@ -275,12 +274,13 @@ def setup_msa_decode(msa, dev, seed, b, kl, hq, hk, topk, splits, fp8):
     return dict(step=step, e2e_step=e2e_step, flops=None, bytes=by_sparse + by_proxy,
                 stages=dict(proxy=(s_proxy, by_proxy, "GB/s"), topk=(s_topk, ms[:, :P].numel() * 4, "GB/s"),
                             sparse=(s_sparse, by_sparse, "GB/s")),
-                metric="msa_decode_kv_gbps", unit="GB/s", bound="hbm", launches=7, graph=True,
+                metric="msa_decode_kv_gbps", unit="GB/s", bound="hbm", launches=4, graph=True,
                 h2d=q_h.numel() * 2, d2h=out_h.numel() * 2,
                 l2="every step streams %.0f MB (proxy cache + selected pages) of a %.1f GB cache: larger than L2" % (
                     (by_sparse + by_proxy) / 1e6, (kp.numel() + vp.numel()) * e / 1e9),
                 cfg=dict(batch_per_gpu=b, q_len=1, kv_len=kl, num_qo_heads=hq, num_kv_heads=hk, topk=topk,
-                         num_kv_splits=splits, kv_dtype="e4m3" if fp8 else "bf16", proxy_heads=1))
+                         num_kv_splits=splits, num_kv_splits_used=plan2[3]["num_kv_splits"],
+                         kv_dtype="e4m3" if fp8 else "bf16", proxy_heads=1))
 
 
 def setup_decode(msa, dev, seed, b, kl, hq, hk, rank=0, world=1):

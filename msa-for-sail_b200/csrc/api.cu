@@ -8,6 +8,8 @@ namespace msa {
 int fmha_mma_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_tc_supported(const MsaFmhaParams& p);
 int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
+int score_gemv_supported(const MsaFmhaParams& p);
+int score_gemv_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_decode_tc_supported(const MsaFmhaParams& p);
 int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_sparse_tc_supported(const MsaFmhaParams& p);
@@ -54,6 +56,7 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (msa::fmha_sparse_tc_supported(p)) return msa::fmha_sparse_tc_launch(p, stream);
+  if (msa::score_gemv_supported(p)) return msa::score_gemv_launch(p, stream);
   if (msa::fmha_decode_tc_supported(p)) return msa::fmha_decode_tc_launch(p, stream);
   if (msa::fmha_tc_supported(p)) return msa::fmha_tc_launch(p, stream);
   return msa::fmha_mma_launch(p, stream);

@@ -18,6 +18,8 @@
 //
 // Output: normalised partial O (fp32) + natural-log LSE per split, or the final bf16 O when the
 // work item is unsplit.  Every wait is bounded (tc_ptx.cuh).
+#include <cstdio>
+
 #include "tc_ptx.cuh"
 
 namespace msa {
@@ -33,25 +35,63 @@ using namespace tc;
 
 constexpr int BM = 128, BN = 128;
 constexpr int SUB_BYTES = BM * 128;             // one [128 rows][128 bytes] swizzled sub-tile
-constexpr int RING_BYTES = 96 * 1024;           // per operand: 3 bf16 tiles or 6 e4m3 tiles
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = 2 * SUB_BYTES;
-constexpr int OFF_V = OFF_K + RING_BYTES;
-constexpr int OFF_BAR = OFF_V + RING_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 1024 + 1024;
 constexpr int NTHREADS = 192;
 constexpr int PRODUCER_WARP = 4, MMA_WARP = 5;
 constexpr int MAX_SPARSE_TILES = 64;
 constexpr int MAX_STAGES = 6;
+constexpr int QUAD_MAX_ROWS = 16;               // rows of a work item the 4-way column split accepts
+constexpr int STAGE_LD = kHeadDim + 4;          // floats per staged O row (padding spreads the banks)
 
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 7, V_FULL = 13, V_EMPTY = 19, S_FULL = 25, P_FULL = 27, PV_DONE = 29,
            V_FIX = 30, NUM_BARS = 31 };
 
-// F8: K/V (and Q, P) are e4m3 and the MMAs are kind::f8f6f4; otherwise bf16 and kind::f16.
-template <bool F8>
-__global__ void __launch_bounds__(NTHREADS, 1)
+// diagnostic timeline: when set, every CTA records 16 words (see msa_debug_decode_trace)
+__device__ unsigned long long* g_trace = nullptr;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Shared / tensor memory plan of one instantiation.
+//   F8    K/V (and Q, P) are e4m3 and the MMAs are kind::f8f6f4; otherwise bf16 and kind::f16.
+//   QUAD  work items of <= 16 rows: the rows are replicated into the four 32-lane quadrants of
+//         the MMA tile and quadrant w runs an independent online softmax over key columns
+//         [32 w, 32 w + 32) of every tile (its P is zero elsewhere), so all four softmax warps
+//         work on a tile instead of the first lanes of one; the four partial (O, m, l) of a row
+//         are combined in shared memory at the end.
+//   F8 && QUAD ("dual"): half the shared memory and 256 TMEM columns, two CTAs per SM, so the
+//         prologue and epilogue of short work items overlap with another item's loads.  The
+//         barriers live in rows 16-31 of the Q tile, which no real row uses.
+template <bool F8, bool QUAD>
+struct Cfg {
+  static constexpr bool DUAL = F8 && QUAD;
+  static constexpr int NSUB = F8 ? 1 : 2;                 // 128-byte-wide sub-tiles per 128 x 128 tile
+  static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
+  static constexpr int RING_BYTES = DUAL ? 48 * 1024 : 96 * 1024;
+  static constexpr int STAGES = RING_BYTES / TILE_BYTES;  // bf16 3, e4m3 6 (dual: 3)
+  static constexpr int OFF_Q = 0;
+  // dual: rows 112-127 of the Q tile are never real rows, the K ring may start there
+  static constexpr int OFF_K = DUAL ? SUB_BYTES - 2048 : 2 * SUB_BYTES;
+  static constexpr int OFF_V = OFF_K + RING_BYTES;
+  static constexpr int END = OFF_V + RING_BYTES;
+  static constexpr int OFF_BAR = DUAL ? 2048 : END;
+  static constexpr int SMEM_BYTES = (DUAL ? END : END + 1024) + 1024;   // + slack to align the base to 1 KB
+  static constexpr int NBUF = DUAL ? 1 : 2;               // S buffers in TMEM
+  static constexpr int TMEM_COLS = DUAL ? 256 : 512;
+  static constexpr int O_COL = NBUF * BN;
+  static constexpr int MIN_CTAS = DUAL ? 2 : 1;
+  static_assert(STAGES <= MAX_STAGES, "barrier table");
+  static_assert(4 * QUAD_MAX_ROWS * STAGE_LD * 4 <= RING_BYTES, "O staging fits the K ring");
+};
+
+template <bool F8, bool QUAD>
+__global__ void __launch_bounds__(NTHREADS, (Cfg<F8, QUAD>::MIN_CTAS))
 decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+  using C = Cfg<F8, QUAD>;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STAGES = C::STAGES, NBUF = C::NBUF;
+  constexpr int OFF_Q = C::OFF_Q, OFF_K = C::OFF_K, OFF_V = C::OFF_V, OFF_BAR = C::OFF_BAR;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -59,11 +99,9 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
   int* s_tiles = reinterpret_cast<int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 16);      // sparse: valid pages, in order
-  int* s_ntiles = s_tiles + MAX_SPARSE_TILES;
+  int* s_phys = s_tiles + MAX_SPARSE_TILES;                                            // ... and their physical ids
+  int* s_ntiles = s_phys + MAX_SPARSE_TILES;
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
-  constexpr int NSUB = F8 ? 1 : 2;                 // 128-byte-wide sub-tiles per 128 x 128 tile
-  constexpr int TILE_BYTES = NSUB * SUB_BYTES;
-  constexpr int STAGES = RING_BYTES / TILE_BYTES;
   constexpr int SUB_ELEMS = F8 ? 128 : 64;          // elements of head_dim per sub-tile
   constexpr int KSTEPS = F8 ? 4 : 8;                // MMAs per 128-deep contraction
   // e4m3 P has 3 mantissa bits: keep it in (2^-6, 2^8] by using the exact running max (no lazy
@@ -72,6 +110,9 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   constexpr float kRescaleThreshold = F8 ? 0.0f : 8.0f;
   constexpr float kPOffset = F8 ? 8.0f : 0.0f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long* trace = (threadIdx.x == 0 && g_trace) ? g_trace + 16ull * blockIdx.x : nullptr;
+  const long long clk0 = clock64();
+  if (trace) { trace[0] = global_ns(); unsigned id; asm("mov.u32 %0, %%smid;" : "=r"(id)); trace[2] = id; }
   const bool sparse = (p.flags & MSA_FLAG_SPARSE) != 0;
   const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;   // false: score-only pass (no V, no P, no O)
   const int G = p.pack;
@@ -79,6 +120,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
 
   // ---------------- work item ----------------
   int b, head0, tb, te, split, i_base, ntok;
+  int blk_first = -1;                       // sparse: this lane's entry of the selected-page list, fetched early
   const int32_t* blocks = nullptr;
   if (!sparse) {
     const MsaWorkItem w = p.work[blockIdx.x];
@@ -91,14 +133,16 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     split = idx % S; idx /= S;
     const int kvh_s = idx % p.num_kv_heads;
     const int t = idx / p.num_kv_heads;
-    b = p.token_batch[t];
-    head0 = kvh_s * h_r;
-    i_base = t - p.qo_start[b];
-    ntok = 1;
     blocks = p.kv_block_indexes + static_cast<int64_t>(t) * p.kbi_stride_tok + static_cast<int64_t>(kvh_s) * p.kbi_stride_head;
     const int per = (p.kv_block_num + S - 1) / S;
     tb = split * per;
     te = min(p.kv_block_num, tb + per);
+    // independent of the batch item: in flight together with the loads below that depend on it
+    if (warp == PRODUCER_WARP && tb + lane < te) blk_first = blocks[tb + lane];
+    b = p.token_batch[t];
+    head0 = kvh_s * h_r;
+    i_base = t - p.qo_start[b];
+    ntok = 1;
   }
   const int kvh = head0 / h_r;
   const int nrows = ntok * G;                                  // real rows of the 128-row tile
@@ -106,7 +150,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const int kv_len = p.kv_len[b];
   const int off = p.qo_offset[b];
   const int page_base = p.kv_page_indptr[b];
-  const int n_active_warps = (nrows + 31) / 32;
+  const int n_active_warps = QUAD ? 4 : (nrows + 31) / 32;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(Q_FULL), F8 ? 32 * n_active_warps : 1);
@@ -114,26 +158,33 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       mbar_init(bar(K_FULL + s), 1);  mbar_init(bar(K_EMPTY + s), 1);
       mbar_init(bar(V_FULL + s), 1);  mbar_init(bar(V_EMPTY + s), 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 32 * n_active_warps); }
+    for (int s = 0; s < NBUF; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 32 * n_active_warps); }
     mbar_init(bar(PV_DONE), 1);
     mbar_init(bar(V_FIX), 1);
     *abort_flag = 0;
     mbar_fence_init();
-    // tile list: dense = [tb, te) of the sequence; sparse = the valid selected pages of this split
+  }
+  if (warp == PRODUCER_WARP) {
+    // tile list: dense = [tb, te) of the sequence; sparse = the valid selected pages of this
+    // split in list order, compacted by the whole warp, with their page-table entries
     if (sparse) {
       int n = 0;
-      const int i_tok = i_base;
-      for (int j = tb; j < te && n < MAX_SPARSE_TILES; ++j) {
-        const int blk = blocks[j];
-        if (blk >= 0 && blk * BN < kv_len && blk * BN <= i_tok + off) s_tiles[n++] = blk;
+      for (int j0 = tb; j0 < te; j0 += 32) {
+        const int j = j0 + lane;
+        const int blk = j0 == tb ? blk_first : (j < te ? blocks[j] : -1);
+        const bool ok = blk >= 0 && blk * BN < kv_len && blk * BN <= i_base + off;
+        const unsigned m = __ballot_sync(0xffffffffu, ok);
+        const int pos = n + __popc(m & ((1u << lane) - 1u));
+        if (ok && pos < MAX_SPARSE_TILES) { s_tiles[pos] = blk; s_phys[pos] = p.kv_indices[page_base + blk]; }
+        n += __popc(m);
       }
-      *s_ntiles = n;
-    } else {
+      if (lane == 0) *s_ntiles = min(n, MAX_SPARSE_TILES);
+    } else if (lane == 0) {
       *s_ntiles = max(0, te - tb);
     }
   }
   if (warp == MMA_WARP) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -141,27 +192,40 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int n_tiles = *s_ntiles;
+  if (trace) trace[3] = clock64() - clk0;
   auto tile_page = [&](int j) -> int { return sparse ? s_tiles[j] : tb + j; };     // logical page of tile j
 
   if (warp == PRODUCER_WARP) {
     // =========================== TMA producer ===========================
     if (lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
     if (n_tiles > 0 && !F8) {                                 // e4m3: the softmax warps convert and place Q
-      if (lane == 0) mbar_arrive_expect_tx(bar(Q_FULL), nrows * 256);
+      constexpr int COPIES = QUAD ? 4 : 1;
+      if (lane == 0) mbar_arrive_expect_tx(bar(Q_FULL), COPIES * nrows * 256);
       __syncwarp();
-      for (int ti = lane; ti < ntok; ti += 32) {             // G rows of one token per box
-        const uint32_t dst = smem_base + OFF_Q + ti * G * 128;
+      for (int c = lane; c < ntok * COPIES; c += 32) {       // G rows of one token per box
+        const int ti = c / COPIES, quad = c % COPIES;
+        const uint32_t dst = smem_base + OFF_Q + (quad * 32 + ti * G) * 128;
         tma_load_3d(dst, &tm_q, bar(Q_FULL), 0, head0, qo_base + i_base + ti);
         tma_load_3d(dst + SUB_BYTES, &tm_q, bar(Q_FULL), 64, head0, qo_base + i_base + ti);
       }
       __syncwarp();
+    }
+    // page-table entries: one per lane, 32 tiles at a time, the next batch already in flight
+    int phys_cur = 0, phys_next = 0;
+    if (!sparse) {
+      phys_cur = lane < n_tiles ? p.kv_indices[page_base + tb + lane] : 0;
+      phys_next = 32 + lane < n_tiles ? p.kv_indices[page_base + tb + 32 + lane] : 0;
     }
     uint32_t fix_phase = 0;
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int st = j % STAGES;
       const int lp = tile_page(j);
-      const int phys = p.kv_indices[page_base + lp];
+      if (!sparse && j > 0 && (j & 31) == 0) {
+        phys_cur = phys_next;
+        phys_next = j + 32 + lane < n_tiles ? p.kv_indices[page_base + tb + j + 32 + lane] : 0;
+      }
+      const int phys = sparse ? s_phys[j] : __shfl_sync(0xffffffffu, phys_cur, j & 31);
       const int valid_rows = min(BN, kv_len - lp * BN);
       const bool fix = valid_rows < BN;
       alive = mbar_wait(bar(K_EMPTY + st), ((j / STAGES) & 1) ^ 1, abort_flag);
@@ -208,13 +272,14 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     const uint64_t dk_hi = smem_desc(0, 16, 1024) & 0xFFFFFFFFFFFF0000ull;
     const uint64_t dv_hi = smem_desc(0, SUB_BYTES, 1024) & 0xFFFFFFFFFFFF0000ull;
     constexpr int V_KSTEP = (BN / KSTEPS) * 128;     // bytes between the key slices of consecutive P.V MMAs
+    auto sbuf = [&](int j) -> uint32_t { return tmem + (j % NBUF) * BN; };
     auto issue_qk = [&](int j) {
       const uint32_t qa = (smem_base + OFF_Q) >> 4, ka = (smem_base + OFF_K + (j % STAGES) * TILE_BYTES) >> 4;
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k) {
         const uint32_t o = ((k >> 2) * SUB_BYTES + (k & 3) * 32) >> 4;      // 32 bytes of head_dim per MMA
-        if constexpr (F8) mma_ss_f8(tmem + (j & 1) * BN, dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
-        else mma_ss(tmem + (j & 1) * BN, dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+        if constexpr (F8) mma_ss_f8(sbuf(j), dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+        else mma_ss(sbuf(j), dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
       }
     };
     auto issue_pv = [&](int j) {
@@ -222,9 +287,22 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k) {                // P: 8 TMEM columns per MMA in both formats
         const uint64_t vd = dv_hi | ((va + k * (V_KSTEP >> 4)) & 0x3FFF);
-        if constexpr (F8) mma_ts_f8(tmem + 256, tmem + (j & 1) * BN + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
-        else mma_ts(tmem + 256, tmem + (j & 1) * BN + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        if constexpr (F8) mma_ts_f8(tmem + C::O_COL, sbuf(j) + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        else mma_ts(tmem + C::O_COL, sbuf(j) + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
       }
+    };
+    // S[j + 1] = Q K_{j+1}^T.  Two S buffers: issued before P_j V_j so it overlaps the softmax of
+    // tile j.  One buffer (dual): issued after P_j V_j, which is what frees the buffer.
+    auto next_qk = [&](int j, bool& alive) {
+      const int st = (j + 1) % STAGES;
+      alive = mbar_wait(bar(K_FULL + st), ((j + 1) / STAGES) & 1, abort_flag);
+      // score-only pass: no P.V orders the reuse of the S buffer, wait for its reader instead
+      if (alive && !has_o && j + 1 >= NBUF)
+        alive = mbar_wait(bar(P_FULL + (j + 1) % NBUF), ((j + 1 - NBUF) / NBUF) & 1, abort_flag);
+      if (!alive) return;
+      tc_fence_after();
+      if (elect_one()) { issue_qk(j + 1); mma_commit(bar(S_FULL + (j + 1) % NBUF)); mma_commit(bar(K_EMPTY + st)); }
+      __syncwarp();
     };
     bool alive = n_tiles > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag) : true;
     if (alive && n_tiles > 0) alive = mbar_wait(bar(K_FULL + 0), 0, abort_flag);
@@ -234,29 +312,23 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       __syncwarp();
     }
     for (int j = 0; j < n_tiles && alive; ++j) {
-      if (j + 1 < n_tiles) {                                 // S[(j+1)&1] = Q K_{j+1}^T while tile j is in softmax
-        const int st = (j + 1) % STAGES;
-        alive = mbar_wait(bar(K_FULL + st), ((j + 1) / STAGES) & 1, abort_flag);
-        // score-only pass: no P.V orders the reuse of the S buffer, wait for its reader instead
-        if (alive && !has_o && j >= 1) alive = mbar_wait(bar(P_FULL + ((j + 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
+      if (NBUF == 2 && j + 1 < n_tiles) { next_qk(j, alive); if (!alive) break; }
+      if (has_o) {
+        alive = mbar_wait(bar(V_FULL + j % STAGES), (j / STAGES) & 1, abort_flag);
+        if (alive) alive = mbar_wait(bar(P_FULL + j % NBUF), (j / NBUF) & 1, abort_flag);
         if (!alive) break;
         tc_fence_after();
-        if (elect_one()) { issue_qk(j + 1); mma_commit(bar(S_FULL + ((j + 1) & 1))); mma_commit(bar(K_EMPTY + st)); }
+        if (elect_one()) { issue_pv(j); mma_commit(bar(V_EMPTY + j % STAGES)); mma_commit(bar(PV_DONE)); }
         __syncwarp();
       }
-      if (!has_o) continue;
-      alive = mbar_wait(bar(V_FULL + j % STAGES), (j / STAGES) & 1, abort_flag);
-      if (alive) alive = mbar_wait(bar(P_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
-      if (!alive) break;
-      tc_fence_after();
-      if (elect_one()) { issue_pv(j); mma_commit(bar(V_EMPTY + j % STAGES)); mma_commit(bar(PV_DONE)); }
-      __syncwarp();
+      if (NBUF == 1 && j + 1 < n_tiles) { next_qk(j, alive); if (!alive) break; }
     }
   } else if (warp < n_active_warps) {
     // =========================== softmax / epilogue ===========================
-    const int r = (warp << 5) | lane;                        // row == TMEM lane
+    const int trow = (warp << 5) | lane;                     // row of the MMA tile == TMEM lane
+    const int r = QUAD ? lane : trow;                        // logical row of the work item
     const uint32_t lane_addr = static_cast<uint32_t>(warp << 5) << 16;
-    const uint32_t tO = tmem + 256 + lane_addr;
+    const uint32_t tO = tmem + C::O_COL + lane_addr;
     const bool row_ok = r < nrows;
     const int i = i_base + (row_ok ? r / G : 0);
     const int head = head0 + (row_ok ? r % G : 0);
@@ -300,17 +372,101 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
             }
           }
         }
+        // QUAD: only the real rows are written (rows 16-31 of the first quadrant hold the
+        // barriers; what the MMA reads from unused rows only reaches unused TMEM lanes)
+        if (!QUAD || row_ok) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(smem_gen + OFF_Q + r * 128 + ((c ^ (r & 7)) << 4)) = chunks[c];
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(smem_gen + OFF_Q + trow * 128 + ((c ^ (trow & 7)) << 4)) = chunks[c];
+        }
         fence_proxy_async_smem();
         mbar_arrive(bar(Q_FULL));
       }
     }
 
+    if constexpr (QUAD) {
+      // quadrant `warp` owns key columns [32 warp, 32 warp + 32) of every tile
+      for (int j = 0; j < n_tiles && alive; ++j) {
+        const uint32_t tS = tmem + (j % NBUF) * BN + lane_addr;
+        alive = mbar_wait(bar(S_FULL + j % NBUF), (j / NBUF) & 1, abort_flag);
+        if (!alive) break;
+        if (trace && j < 4) trace[4 + j] = clock64() - clk0;
+        tc_fence_after();
+        const int pos0 = tile_page(j) * BN + warp * 32;
+        uint32_t sv[32];
+        tmem_ld32(tS + warp * 32, sv);
+        tmem_wait_ld();
+        if (pos0 + 31 > lim) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (pos0 + e > lim) sv[e] = 0xff800000u;
+        }
+        float mxs[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < 32; e += 2)
+          mxs[(e >> 1) & 1] = max3(mxs[(e >> 1) & 1], __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
+        const float mx = fmaxf(mxs[0], mxs[1]);
+        const float m_cand = fmaxf(m_used, mx * scale_log2);
+        const bool bump = (m_cand - m_used) > kRescaleThreshold;
+        float factor = 1.f;
+        if (bump) { factor = exp2_fast(m_used - m_cand); m_used = m_cand; l_sum *= factor; }
+        if (j > 0 && __any_sync(0xffffffffu, bump)) {
+          alive = mbar_wait(bar(PV_DONE), (j - 1) & 1, abort_flag);
+          if (!alive) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tO + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+            tmem_st32(tO + c * 32, v);
+          }
+        }
+        const float msafe = ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset;
+        float l0 = 0.f, l1 = 0.f;
+        constexpr int PCOLS = F8 ? 8 : 16;                   // TMEM columns of P per 32 keys
+        uint32_t pk[PCOLS], zero[PCOLS];
+#pragma unroll
+        for (int e = 0; e < PCOLS; ++e) zero[e] = 0u;
+        if constexpr (F8) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float p0 = exp2_fast(fmaf(__uint_as_float(sv[e]), scale_log2, -msafe));
+            const float p1 = exp2_fast(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -msafe));
+            const float p2 = exp2_fast(fmaf(__uint_as_float(sv[e + 2]), scale_log2, -msafe));
+            const float p3 = exp2_fast(fmaf(__uint_as_float(sv[e + 3]), scale_log2, -msafe));
+            l0 += p0 + p2; l1 += p1 + p3;
+            const uint16_t lo = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
+            const uint16_t hi = __nv_cvt_float2_to_fp8x2(make_float2(p2, p3), __NV_SATFINITE, __NV_E4M3);
+            pk[e >> 2] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = exp2_fast(fmaf(__uint_as_float(sv[e]), scale_log2, -msafe));
+            const float p1 = exp2_fast(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -msafe));
+            l0 += p0; l1 += p1;
+            pk[e >> 1] = pack2<false>(p0, p1);
+          }
+        }
+        // P of this quadrant's rows: own 32 keys, zero for the other 96
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if constexpr (F8) { if (q == warp) tmem_st8(tS + q * PCOLS, pk); else tmem_st8(tS + q * PCOLS, zero); }
+          else { if (q == warp) tmem_st16(tS + q * PCOLS, pk); else tmem_st16(tS + q * PCOLS, zero); }
+        }
+        l_sum += l0 + l1;
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(P_FULL + j % NBUF));
+        if (trace && j == n_tiles - 1) trace[8] = clock64() - clk0;
+      }
+    } else {
     for (int j = 0; j < n_tiles && alive; ++j) {
-      const uint32_t tS = tmem + (j & 1) * BN + lane_addr;
-      alive = mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
+      const uint32_t tS = tmem + (j % NBUF) * BN + lane_addr;
+      alive = mbar_wait(bar(S_FULL + j % NBUF), (j / NBUF) & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
       const int pos0 = tile_page(j) * BN;
@@ -344,7 +500,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       }
       if (!has_o) {                      // score-only pass: S is consumed, hand the buffer back
         tc_fence_before();
-        mbar_arrive(bar(P_FULL + (j & 1)));
+        mbar_arrive(bar(P_FULL + j % NBUF));
         continue;
       }
       const float m_cand = fmaxf(m_used, mx * scale_log2);
@@ -399,11 +555,95 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       l_sum += l0 + l1;
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(P_FULL + (j & 1)));
+      mbar_arrive(bar(P_FULL + j % NBUF));
+    }
+
     }
 
     // ---- epilogue ----
     if (alive && n_tiles > 0 && has_o) alive = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, abort_flag);
+    if (trace) trace[9] = clock64() - clk0;
+    if constexpr (QUAD) {
+      // every MMA and every TMA load of this CTA has completed: the K ring is free to stage the
+      // four partial results of each row; thread t then combines column t of every row
+      float* stage = reinterpret_cast<float*>(smem_gen + OFF_K);              // [4][nrows][STAGE_LD]
+      float* st_m = reinterpret_cast<float*>(smem_gen + OFF_V);               // [4][QUAD_MAX_ROWS]
+      float* st_l = st_m + 4 * QUAD_MAX_ROWS;
+      alive = __all_sync(0xffffffffu, alive);
+      if (alive && has_o) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          if (n_tiles > 0) {
+            tmem_ld32(tO + c * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0u;
+          }
+          if (row_ok) {
+            float* dst = stage + (warp * nrows + r) * STAGE_LD + c * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<float4*>(dst + e) = make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]),
+                                                                __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+          }
+        }
+        if (row_ok) { st_m[warp * QUAD_MAX_ROWS + r] = m_used; st_l[warp * QUAD_MAX_ROWS + r] = l_sum; }
+      }
+      if (trace) trace[10] = clock64() - clk0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (trace) trace[11] = clock64() - clk0;
+      if (*abort_flag == 0 && has_o) {
+        // thread -> (row, 8 columns): 16 threads per row, 8 rows per pass; the weights of a row
+        // are computed once per thread
+        const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
+        const bool to_partial = p.partial_o != nullptr;
+        const int c8 = (trow & 15) * 8;
+        for (int rr = trow >> 4; rr < nrows; rr += 8) {
+          float mq[4], wq[4], M = -INFINITY, L = 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) { mq[q] = st_m[q * QUAD_MAX_ROWS + rr]; M = fmaxf(M, mq[q]); }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            wq[q] = (mq[q] == -INFINITY) ? 0.f : exp2_fast(mq[q] - M);
+            L += st_l[q * QUAD_MAX_ROWS + rr] * wq[q];
+          }
+          const float inv = L > 0.f ? __fdividef(to_partial ? vsh : p.out_scale * vsh, L) : 0.f;
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 a0 = *reinterpret_cast<const float4*>(stage + (q * nrows + rr) * STAGE_LD + c8);
+            const float4 a1 = *reinterpret_cast<const float4*>(stage + (q * nrows + rr) * STAGE_LD + c8 + 4);
+            const float w = wq[q] * inv;                      // a quadrant that saw no key has weight 0 and O == 0
+            acc[0] = fmaf(a0.x, w, acc[0]); acc[1] = fmaf(a0.y, w, acc[1]); acc[2] = fmaf(a0.z, w, acc[2]); acc[3] = fmaf(a0.w, w, acc[3]);
+            acc[4] = fmaf(a1.x, w, acc[4]); acc[5] = fmaf(a1.y, w, acc[5]); acc[6] = fmaf(a1.z, w, acc[6]); acc[7] = fmaf(a1.w, w, acc[7]);
+          }
+          const int gt = qo_base + i_base + rr / G, hd = head0 + rr % G;
+          const float lse = L > 0.f ? (M - kPOffset) * kLn2 + __logf(L) : -INFINITY;   // l carries 2^kPOffset
+          const int64_t prow = (static_cast<int64_t>(split) * p.total_q + gt) * p.num_qo_heads + hd;
+          if (to_partial) {
+            float* dst = p.partial_o + prow * kHeadDim + c8;
+            *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            if (c8 == 0) p.partial_lse[prow] = lse;
+          } else {
+            if (p.out) {
+              uint4 o4;
+              o4.x = pack2<false>(acc[0], acc[1]); o4.y = pack2<false>(acc[2], acc[3]);
+              o4.z = pack2<false>(acc[4], acc[5]); o4.w = pack2<false>(acc[6], acc[7]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(gt) * p.out_stride_tok +
+                                        static_cast<int64_t>(hd) * p.out_stride_head + c8) = o4;
+            }
+            if (c8 == 0 && p.lse) p.lse[static_cast<int64_t>(gt) * p.num_qo_heads + hd] = lse;
+          }
+        }
+      }
+      if (trace) trace[12] = clock64() - clk0;
+    } else
     if (alive && has_o) {
       tc_fence_after();
       const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
@@ -453,9 +693,10 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0 && p.status) atomicExch(p.status, MSA_STATUS_TIMEOUT);
+  if (trace) { trace[13] = clock64() - clk0; trace[1] = global_ns(); }
   if (warp == MMA_WARP) {
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, C::TMEM_COLS);
   }
 }
 
@@ -512,17 +753,66 @@ int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
         return MSA_ERR_LAUNCH;
     }
   }
-  static bool attr_done[16][2] = {};
+  // the 4-way column split needs O (its quadrants do not share a row max) and <= 16 rows
+  const bool quad = has_o && p.decode_rows <= QUAD_MAX_ROWS;
+  static bool attr_done[16][4] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = f8 ? decode_tc_kernel<true> : decode_tc_kernel<false>;
-  if (dev >= 16 || !attr_done[dev][f8]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return MSA_ERR_LAUNCH;
-    if (dev < 16) attr_done[dev][f8] = true;
+  using Kern = void (*)(const MsaFmhaParams, const CUtensorMap, const CUtensorMap, const CUtensorMap);
+  const int variant = (f8 ? 2 : 0) | (quad ? 1 : 0);
+  Kern kern;
+  int smem;
+  switch (variant) {
+    case 0: kern = decode_tc_kernel<false, false>; smem = Cfg<false, false>::SMEM_BYTES; break;
+    case 1: kern = decode_tc_kernel<false, true>;  smem = Cfg<false, true>::SMEM_BYTES;  break;
+    case 2: kern = decode_tc_kernel<true, false>;  smem = Cfg<true, false>::SMEM_BYTES;  break;
+    default: kern = decode_tc_kernel<true, true>;  smem = Cfg<true, true>::SMEM_BYTES;   break;
   }
-  kern<<<static_cast<unsigned>(grid64), NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv);
+  if (dev >= 16 || !attr_done[dev][variant]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return MSA_ERR_LAUNCH;
+    if (variant == 3)      // two co-resident CTAs need the whole shared-memory carve-out
+      cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (dev < 16) attr_done[dev][variant] = true;
+  }
+  kern<<<static_cast<unsigned>(grid64), NTHREADS, smem, stream>>>(p, tq, tk, tv);
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
 }
 
+// CTAs of one decode-kernel variant that fit an SM (what the occupancy calculator reports).
+int fmha_decode_tc_occupancy(int f8, int quad) {
+  using namespace decode_tc;
+  int n = 0;
+  cudaError_t e;
+  if (f8 && quad) {
+    cudaFuncSetAttribute(decode_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true, true>::SMEM_BYTES);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_tc_kernel<true, true>, NTHREADS, Cfg<true, true>::SMEM_BYTES);
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, decode_tc_kernel<true, true>) == cudaSuccess)
+      fprintf(stderr, "decode_tc_kernel<e4m3, quad>: regs %d static smem %zu dyn smem %d local %zu max threads %d\n", fa.numRegs,
+              fa.sharedSizeBytes, Cfg<true, true>::SMEM_BYTES, fa.localSizeBytes, fa.maxThreadsPerBlock);
+  } else if (f8) {
+    cudaFuncSetAttribute(decode_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true, false>::SMEM_BYTES);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_tc_kernel<true, false>, NTHREADS, Cfg<true, false>::SMEM_BYTES);
+  } else if (quad) {
+    cudaFuncSetAttribute(decode_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false, true>::SMEM_BYTES);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_tc_kernel<false, true>, NTHREADS, Cfg<false, true>::SMEM_BYTES);
+  } else {
+    cudaFuncSetAttribute(decode_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false, false>::SMEM_BYTES);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_tc_kernel<false, false>, NTHREADS, Cfg<false, false>::SMEM_BYTES);
+  }
+  return e == cudaSuccess ? n : -1;
+}
+
 }  // namespace msa
+
+// diagnostic, not part of the documented ABI: resident CTAs per SM of a decode-kernel variant
+extern "C" int msa_debug_decode_occupancy(int f8, int quad) { return msa::fmha_decode_tc_occupancy(f8, quad); }
+
+// diagnostic, not part of the documented ABI: device buffer of 16 x uint64 per CTA, or NULL to stop
+// [0] start ns  [1] end ns  [2] SM id; clocks since entry: [3] prologue done, [4..7] S of tiles 0-3
+// ready, [8] last P written, [9] last P.V done, [10] O staged, [11] staging barrier passed,
+// [12] rows combined and stored, [13] exit
+extern "C" void msa_debug_decode_trace(unsigned long long* device_buf) {
+  cudaMemcpyToSymbol(msa::decode_tc::g_trace, &device_buf, sizeof(device_buf));
+}

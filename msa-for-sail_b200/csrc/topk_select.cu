@@ -155,6 +155,83 @@ topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
   }
 }
 
+// Few rows (decode): one CTA per (token, head) row, its 256 threads share the row's pages, NK
+// per thread, kept in registers as order keys.  TOPK rounds: every thread offers its best key
+// below the previous winner, warps reduce with redux.sync, the CTA through shared memory.  The
+// order is the same strict total order (key desc, page asc), so the result is identical to the
+// thread-per-row kernel above.
+template <int TOPK, int NK, typename T>
+__global__ void __launch_bounds__(256)
+topk_row_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles, int total_q,
+                int nvp, int force_begin, int force_end_start) {
+  __shared__ uint32_t s_ord[2][8], s_page[2][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t = blockIdx.x % total_q, head = blockIdx.x / total_q;
+  const T* base = scores + static_cast<size_t>(head) * max_k_tiles * total_q + t;
+  uint32_t ord[NK];
+#pragma unroll
+  for (int i = 0; i < NK; ++i) {
+    const int page = tid + 256 * i;
+    ord[i] = 0u;                                             // 0: not a candidate
+    if (page < nvp) {
+      const bool forced = page < force_begin || page >= force_end_start;
+      ord[i] = forced ? kForcedOrd : ord_key(static_cast<float>(base[static_cast<size_t>(page) * total_q]));
+    }
+  }
+  uint32_t last_ord = 0xffffffffu;
+  int last_page = -1;
+  uint32_t sel[TOPK];
+#pragma unroll
+  for (int r = 0; r < TOPK; ++r) {
+    uint32_t bo = 0u, bp = 0xffffffffu;
+#pragma unroll
+    for (int i = 0; i < NK; ++i) {                           // pages ascend with i: strict > keeps the lowest page of a tie
+      const int page = tid + 256 * i;
+      const bool below = ord[i] < last_ord || (ord[i] == last_ord && page > last_page);
+      if (below && ord[i] > bo) { bo = ord[i]; bp = static_cast<uint32_t>(page); }
+    }
+    const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
+    const uint32_t wp = __reduce_min_sync(0xffffffffu, (bo == wo && bo != 0u) ? bp : 0xffffffffu);
+    if (lane == 0) { s_ord[r & 1][warp] = wo; s_page[r & 1][warp] = wp; }
+    __syncthreads();
+    uint32_t go = 0u, gp = 0xffffffffu;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t o = s_ord[r & 1][w], pg = s_page[r & 1][w];
+      if (o > go || (o == go && pg < gp)) { go = o; gp = pg; }
+    }
+    sel[r] = go != 0u ? gp : 0xffffffffu;
+    if (go != 0u) { last_ord = go; last_page = static_cast<int>(gp); }
+    else { last_ord = 0u; last_page = 0x7fffffff; }          // nothing left: later rounds find nothing either
+  }
+  if (tid != 0) return;
+  // ascending page order, -1 (0xffffffff) last
+#pragma unroll
+  for (int k = 2; k <= TOPK; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+      for (int i = 0; i < TOPK; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const uint32_t a = sel[i], b = sel[l];
+          const bool up = (i & k) == 0;
+          sel[i] = up ? min(a, b) : max(a, b);
+          sel[l] = up ? max(a, b) : min(a, b);
+        }
+      }
+    }
+  }
+  int32_t* dst = out + (static_cast<size_t>(t) * num_heads + head) * TOPK;
+#pragma unroll
+  for (int i = 0; i < TOPK; i += 4) {
+    int4 v;
+    v.x = static_cast<int32_t>(sel[i]); v.y = static_cast<int32_t>(sel[i + 1]);
+    v.z = static_cast<int32_t>(sel[i + 2]); v.w = static_cast<int32_t>(sel[i + 3]);
+    *reinterpret_cast<int4*>(dst + i) = v;
+  }
+}
+
 template <int TOPK>
 __global__ void topk_identity_kernel(int32_t* __restrict__ out, size_t rows, int nvp) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -173,6 +250,13 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
     return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
   }
   const int fe_start = fe <= nvp ? nvp - fe : 0;
+  if (rows <= 2048 && nvp <= 256 * 32) {                     // decode-sized: a CTA per row
+    if (nvp <= 256 * 8)
+      topk_row_kernel<TOPK, 8, T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
+    else
+      topk_row_kernel<TOPK, 32, T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
+    return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
+  }
   const int tok_blocks = (T_ + 31) / 32;
   const long long ctas = static_cast<long long>(tok_blocks) * H;
   // enough slices to put ~16 warps on every SM, bounded by the pages there are to scan

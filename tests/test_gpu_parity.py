@@ -87,6 +87,16 @@ def test_topk_golden_distributions_bitexact():
     (3, 128, 5, 9, 16, 0, 0, torch.float32),       # nvp <= topk: identity + -1 padding
     (3, 128, 5, 16, 16, 0, 0, torch.bfloat16),
     (2, 128, 7, 17, 16, 0, 0, torch.float32),
+    # more than 2048 rows: the thread-per-row kernel (fewer rows take the CTA-per-row kernel)
+    (4, 256, 1024, 200, 16, 3, 2, torch.float32),
+    (2, 2048, 1100, 2000, 16, 2, 3, torch.float32),
+    (2, 384, 1200, 300, 32, 2, 2, torch.float32),
+    (8, 128, 300, 77, 8, 0, 0, torch.float32),
+    (2, 128, 1500, 128, 4, 1, 1, torch.bfloat16),
+    # CTA-per-row kernel with more than 2048 pages (32 keys per thread)
+    (1, 4096, 8, 4000, 16, 1, 1, torch.float32),
+    (1, 8192, 4, 8192, 32, 0, 0, torch.bfloat16),
+    (2, 2304, 3, 2100, 8, 0, 2, torch.float32),
 ])
 def test_topk_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
     api = _api()
@@ -439,6 +449,29 @@ def test_proxy_decode_scores_paged(fp8, kernel_path):
     out, ms = api.fmha_sail(qd, kd, kd, plan, kv_indices=table.to(DEV), output_o=False)
     assert out is None
     check_score(ms, orc.tile_max_score(qf, k, qo_lens, kv_lens, hk, ms.shape[1]), "proxy-decode-ms")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("hq,qo_lens", [(1, [1, 1, 1]), (2, [1, 1, 2]), (4, [1, 1, 1]), (1, [3, 4, 1]), (3, [1, 1, 1])])
+def test_proxy_scores_few_rows(fp8, hq, qo_lens):
+    """Score-only pass whose work items have at most four rows: the matrix-vector kernel
+    (ragged last pages, two-token items whose rows see different key limits)."""
+    api = _api()
+    g = gen(91 + fp8 + hq)
+    kv_lens, hk = [1500, 128, 700], 1
+    q = randn_bf16(g, sum(qo_lens), hq, 128)
+    kp, _, table = make_paged(g, kv_lens, hk, 128)
+    if fp8:
+        q8, qf = orc.quantize_e4m3(q); k8, kf = orc.quantize_e4m3(kp)
+        qd, kd = q8.to(DEV), k8.to(DEV)
+    else:
+        qf, kf, qd, kd = q, kp, q.to(DEV), kp.to(DEV)
+    k = orc.paged_to_contiguous(kf, table, kv_lens, 128)
+    plan = api.fmha_sail_plan(_i32(qo_lens), _i32(kv_lens), hq, num_kv_heads=hk, page_size=128,
+                              output_maxscore=True, use_fp8_kvcache=fp8)
+    out, ms = api.fmha_sail(qd, kd, kd, plan, kv_indices=table.to(DEV), output_o=False)
+    assert out is None
+    check_score(ms, orc.tile_max_score(qf, k, qo_lens, kv_lens, hk, ms.shape[1]), "proxy-few-rows-ms")
 
 
 # ---------------------------------------------------------------------------
