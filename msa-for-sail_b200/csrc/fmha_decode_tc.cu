@@ -161,7 +161,8 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     for (int s = 0; s < NBUF; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 32 * n_active_warps); }
     mbar_init(bar(PV_DONE), 1);
     mbar_init(bar(V_FIX), 1);
-    *abort_flag = 0;
+    // a timeout reported earlier on this device (status word not cleared yet): do not start
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
   }
   if (warp == PRODUCER_WARP) {
@@ -195,7 +196,10 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   if (trace) trace[3] = clock64() - clk0;
   auto tile_page = [&](int j) -> int { return sparse ? s_tiles[j] : tb + j; };     // logical page of tile j
 
-  if (warp == PRODUCER_WARP) {
+  const bool run = *abort_flag == 0;
+  if (!run) {
+    // nothing: fall through to the teardown
+  } else if (warp == PRODUCER_WARP) {
     // =========================== TMA producer ===========================
     if (lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
     if (n_tiles > 0 && !F8) {                                 // e4m3: the softmax warps convert and place Q

@@ -106,7 +106,8 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       mbar_init(bar(O_FULL + s), 1);
     }
     mbar_init(bar(V_FIX), 1);
-    *abort_flag = 0;
+    // a timeout reported earlier on this device (status word not cleared yet): do not start
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
   }
   if (warp == MMA_WARP) {
@@ -118,7 +119,10 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == PRODUCER_WARP) {
+  const bool run = *abort_flag == 0;
+  if (!run) {
+    // nothing: fall through to the teardown
+  } else if (warp == PRODUCER_WARP) {
     // =========================== TMA producer ===========================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
