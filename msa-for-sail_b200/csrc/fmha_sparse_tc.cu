@@ -72,7 +72,7 @@ struct Ws {                 // device workspace carved by carve()
   int32_t* bin_count;       // [NB + 1]
   int32_t* bin_offset;      // [NB + 1]  start of a bin in `entries`, a multiple of the tokens per chunk
   int32_t* bin_cursor;      // [NB]
-  int32_t* item_count;      // [1]
+  int32_t* part_start;      // [Hkv + 1]  first work item of every kv head, then the item count
   int4* items;              // [max_items] {bin, entry_begin, entry_end, 0}
   int32_t* entries;         // [cap]  token << 5 | slot, sorted by (kv head, page); gaps between bins are padding
   int32_t* inv;             // [T, Hkv, kbn]  position of a selection in `entries`, -1 if it selects nothing
@@ -96,7 +96,7 @@ Ws carve(void* base, int64_t T, int Hq, int Hkv, int kbn, int64_t NP) {
   int64_t off = 0;
   auto take = [&](int64_t bytes) { char* r = p ? p + off : nullptr; off = align256(off + bytes); return r; };
   w.bin_count = reinterpret_cast<int32_t*>(take((NB + 1) * 4));
-  w.item_count = reinterpret_cast<int32_t*>(take(256));
+  w.part_start = reinterpret_cast<int32_t*>(take((Hkv + 1) * 4));
   // everything above is zeroed before each run
   w.bin_offset = reinterpret_cast<int32_t*>(take((NB + 1) * 4));
   w.bin_cursor = reinterpret_cast<int32_t*>(take(NB * 4));
@@ -156,11 +156,66 @@ sparse_index_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t*
   }
 }
 
+// The same two passes with a shared-memory histogram: a CTA owns 256 consecutive tokens of one kv
+// head, counts (or ranks) its selections per page in shared memory and touches global memory once
+// per (CTA, page) -- the global atomics drop from one per selection to one per distinct page of a
+// CTA.  Needs num_pages * 4 bytes of shared memory; larger page counts use the kernel above.
+template <bool SCATTER, int KBN>
+__global__ void __launch_bounds__(256)
+sparse_index_smem_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t* __restrict__ bin_cursor,
+                         int32_t* __restrict__ entries, int32_t* __restrict__ inv) {
+  extern __shared__ int32_t s_hist[];                      // [num_pages] count, then (scatter) next position
+  const int blocks_per_head = (a.total_q + 255) / 256;
+  const int kvh = blockIdx.x / blocks_per_head;
+  const int t = (blockIdx.x % blocks_per_head) * 256 + threadIdx.x;
+  for (int i = threadIdx.x; i < a.num_pages; i += 256) s_hist[i] = 0;
+  __syncthreads();
+  int gpage[KBN];                                           // global page of each valid selection, -1 otherwise
+#pragma unroll
+  for (int s = 0; s < KBN; ++s) gpage[s] = -1;
+  if (t < a.total_q) {
+    const int b = a.token_batch[t];
+    const int page_base = a.kv_page_indptr[b];
+    const int32_t* row = a.kbi + static_cast<int64_t>(t) * a.kbi_stride_tok + static_cast<int64_t>(kvh) * a.kbi_stride_head;
+#pragma unroll
+    for (int s = 0; s < KBN; ++s) {
+      if (s < a.kbn) {
+        const int blk = row[s];
+        if (entry_valid(a, t, b, blk)) { gpage[s] = page_base + blk; atomicAdd(&s_hist[gpage[s]], 1); }
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < a.num_pages; i += 256) {
+    const int c = s_hist[i];
+    if (c > 0) {
+      if (SCATTER) s_hist[i] = atomicAdd(&bin_cursor[kvh * a.num_pages + i], c);   // reserve c consecutive positions
+      else atomicAdd(&bin_count[kvh * a.num_pages + i], c);
+    }
+  }
+  if (!SCATTER) return;
+  __syncthreads();
+  if (t < a.total_q) {
+    int32_t* inv_row = inv + (static_cast<int64_t>(t) * a.num_kv_heads + kvh) * a.kbn;
+#pragma unroll
+    for (int s = 0; s < KBN; ++s) {
+      if (s < a.kbn) {
+        int pos = -1;
+        if (gpage[s] >= 0) {
+          pos = atomicAdd(&s_hist[gpage[s]], 1);
+          entries[pos] = (t << 5) | s;
+        }
+        inv_row[s] = pos;
+      }
+    }
+  }
+}
+
 // exclusive scan of the bin counts + work items (one CTA; NB is a few thousand to ~1e5)
 __global__ void __launch_bounds__(1024)
 sparse_scan_kernel(const int32_t* __restrict__ bin_count, int32_t* __restrict__ bin_offset,
-                   int32_t* __restrict__ bin_cursor, int4* __restrict__ items, int32_t* __restrict__ item_count,
-                   int num_bins, int rows_per_item, int max_items, int tpc) {
+                   int32_t* __restrict__ bin_cursor, int4* __restrict__ items, int32_t* __restrict__ part_start,
+                   int num_bins, int rows_per_item, int max_items, int tpc, int bins_per_head) {
   __shared__ int s_ent[1024], s_itm[1024];
   __shared__ int carry_ent, carry_itm;
   if (threadIdx.x == 0) { carry_ent = 0; carry_itm = 0; }
@@ -182,6 +237,7 @@ sparse_scan_kernel(const int32_t* __restrict__ bin_count, int32_t* __restrict__ 
     const int ent0 = carry_ent + s_ent[threadIdx.x] - cnt_pad;
     const int itm0 = carry_itm + s_itm[threadIdx.x] - nit;
     if (bin < num_bins) {
+      if (bin % bins_per_head == 0) part_start[bin / bins_per_head] = min(itm0, max_items);
       bin_offset[bin] = ent0;
       bin_cursor[bin] = ent0;
       for (int k = 0; k < nit; ++k)
@@ -192,7 +248,7 @@ sparse_scan_kernel(const int32_t* __restrict__ bin_count, int32_t* __restrict__ 
     if (threadIdx.x == 1023) { carry_ent += s_ent[1023]; carry_itm += s_itm[1023]; }
     __syncthreads();
   }
-  if (threadIdx.x == 0) { bin_offset[num_bins] = carry_ent; *item_count = min(carry_itm, max_items); }
+  if (threadIdx.x == 0) { bin_offset[num_bins] = carry_ent; part_start[num_bins / bins_per_head] = min(carry_itm, max_items); }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -204,16 +260,19 @@ template <int KBN>
 __global__ void __launch_bounds__(256)
 sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restrict__ pl, const int32_t* __restrict__ inv,
                     __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int kbn, int total_q, int num_heads,
-                    int num_kv_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale) {
+                    int num_kv_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale, int kvh0, int nkvh) {
   const int l16 = threadIdx.x & 15;
   // rows are walked kv-head-major: the partials of one kv head are one contiguous eighth (1 / Hkv) of
-  // the buffer, which keeps the randomly gathered 2 KB reads of a pass within reach of the TLB
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4);   // (kvh * T + t) * G + g
-  if (idx >= static_cast<int64_t>(total_q) * num_heads) return;
+  // the buffer, which keeps the randomly gathered 2 KB reads of a pass within reach of the TLB.
+  // This launch covers kv heads [kvh0, kvh0 + nkvh); a small grid strides over them (used while the
+  // attention kernel of the next kv head runs on the other SMs).
   const int G = num_heads / num_kv_heads;
+  const int64_t n_idx = static_cast<int64_t>(total_q) * G * nkvh;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4); idx < n_idx;
+       idx += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 4)) {
   const int g = static_cast<int>(idx % G);
   const int64_t tg = idx / G;
-  const int kvh = static_cast<int>(tg / total_q), t = static_cast<int>(tg % total_q);
+  const int kvh = kvh0 + static_cast<int>(tg / total_q), t = static_cast<int>(tg % total_q);
   const int h = kvh * G + g;
   const int64_t row = static_cast<int64_t>(t) * num_heads + h;
   const int32_t* iv = inv + (static_cast<int64_t>(t) * num_kv_heads + kvh) * kbn;
@@ -256,6 +315,7 @@ sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restric
   pk.w = pack2<false>(acc[6] * sc, acc[7] * sc);
   *reinterpret_cast<uint4*>(dst) = pk;
   if (lse_out && l16 == 0) lse_out[row] = sw > 0.f ? mxs + __logf(sw) : -INFINITY;
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -264,9 +324,12 @@ sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restric
 __global__ void __launch_bounds__(NTHREADS, 1)
 sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                 const __grid_constant__ CUtensorMap tm_o, const int4* __restrict__ items, const int32_t* __restrict__ item_count,
+                 const __grid_constant__ CUtensorMap tm_o, const int4* __restrict__ items, const int32_t* __restrict__ part_start,
+                 const int part,
                  const int32_t* __restrict__ entries, float* __restrict__ partial_lse) {
-  if (static_cast<int>(blockIdx.x) >= *item_count) return;       // uniform: before any barrier / TMEM use
+  // this launch covers the work items of kv head `part`, or all of them (part < 0)
+  const int item_idx = (part >= 0 ? part_start[part] : 0) + static_cast<int>(blockIdx.x);
+  if (item_idx >= part_start[part >= 0 ? part + 1 : p.num_kv_heads]) return;   // uniform: before any barrier / TMEM use
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -281,7 +344,7 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   };
 
   // ---------------- work item ----------------
-  const int4 item = items[blockIdx.x];
+  const int4 item = items[item_idx];
   const int NP = p.num_logical_pages;
   const int kvh = item.x / NP, gp = item.x % NP;
   const int b = p.page_batch[gp];
@@ -674,11 +737,27 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   const int64_t n_thr = static_cast<int64_t>(p.total_q) * p.num_kv_heads;
   const unsigned n_blk = static_cast<unsigned>((n_thr + 255) / 256);
   const int tpc = BM / G;
-  sparse_index_kernel<false><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
   const int rows_per_item = tpc * ITEM_CHUNKS;
-  sparse_scan_kernel<<<1, 1024, 0, stream>>>(w.bin_count, w.bin_offset, w.bin_cursor, w.items, w.item_count,
-                                             static_cast<int>(NB), rows_per_item, static_cast<int>(w.max_items), tpc);
-  sparse_index_kernel<true><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+  const size_t hist_bytes = static_cast<size_t>(NP) * 4;
+  const bool smem_hist = hist_bytes <= 48 * 1024;
+  const unsigned n_blk_s = static_cast<unsigned>((p.total_q + 255) / 256) * p.num_kv_heads;
+  auto index_pass = [&](bool scatter) {
+    if (!smem_hist) {
+      if (scatter) sparse_index_kernel<true><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+      else sparse_index_kernel<false><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+    } else if (p.kv_block_num <= 16) {
+      if (scatter) sparse_index_smem_kernel<true, 16><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+      else sparse_index_smem_kernel<false, 16><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+    } else {
+      if (scatter) sparse_index_smem_kernel<true, 32><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+      else sparse_index_smem_kernel<false, 32><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+    }
+  };
+  index_pass(false);
+  sparse_scan_kernel<<<1, 1024, 0, stream>>>(w.bin_count, w.bin_offset, w.bin_cursor, w.items, w.part_start,
+                                             static_cast<int>(NB), rows_per_item, static_cast<int>(w.max_items), tpc,
+                                             static_cast<int>(NP));
+  index_pass(true);
   if (cudaGetLastError() != cudaSuccess) return MSA_ERR_LAUNCH;
 
   // 2. attention over (page, token chunk) items
@@ -717,11 +796,14 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
       return MSA_ERR_LAUNCH;
     if (dev < 16) attr_done[dev] = true;
   }
-  sparse_tc_kernel<<<static_cast<unsigned>(w.max_items), NTHREADS, SMEM_BYTES, stream>>>(
-      p, tq, tk, tv, to, w.items, w.item_count, w.entries, w.partial_lse);
+  sparse_tc_kernel<<<static_cast<unsigned>(w.max_items), NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv, to, w.items, w.part_start,
+                                                                                     -1, w.entries, w.partial_lse);
   if (cudaGetLastError() != cudaSuccess) return MSA_ERR_LAUNCH;
 
-  // 3. merge the kv_block_num partials of every (token, head)
+  // 3. merge the kv_block_num partials of every (token, head).  (Running the merge of kv head k on a
+  // second stream with a small grid while the attention kernel works on head k + 1 was tried: an SM
+  // sustains ~60 GB/s of gathered reads with its registers as the only landing space, so the merge
+  // needs a third of the SMs to keep up and the attention kernel loses more than the merge gains.)
   const int64_t rows = static_cast<int64_t>(p.total_q) * p.num_qo_heads;
   const int64_t blocks = (rows + 15) / 16;
   if (blocks > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
@@ -729,7 +811,7 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 #define MSA_MERGE(KK)                                                                                             \
   sparse_merge_kernel<KK><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                                    \
       w.partial_o, w.partial_lse, w.inv, outp, p.lse, p.kv_block_num, p.total_q, p.num_qo_heads, p.num_kv_heads, \
-      p.out_stride_tok, p.out_stride_head, p.out_scale)
+      p.out_stride_tok, p.out_stride_head, p.out_scale, 0, p.num_kv_heads)
   if (p.kv_block_num <= 8) MSA_MERGE(8);
   else if (p.kv_block_num <= 16) MSA_MERGE(16);
   else MSA_MERGE(32);

@@ -300,12 +300,11 @@ def _fmha_sail_plan(
     if is_sparse:
         items = total_q * hkv
         if num_kv_splits >= 1:
-            # an explicit count is an upper bound: once the (token, KV head) items alone fill the
-            # resident CTA slots, further splitting only adds per-CTA prologue/epilogue latency
-            # and a merge pass (the result does not depend on the split count)
+            # an explicit count is an upper bound: once the (token, KV head) items alone give every
+            # SM a CTA, further splitting only adds per-CTA prologue/epilogue latency and a merge
+            # pass (the result does not depend on the split count)
             splits = min(num_kv_splits, kv_block_num)
-            slots = num_sms * (2 if use_fp8_kvcache else 1)
-            while splits > 1 and items * (splits // 2) >= slots:
+            while splits > 1 and items * (splits // 2) >= num_sms:
                 splits //= 2
         else:
             splits = 1
