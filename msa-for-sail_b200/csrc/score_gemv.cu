@@ -5,7 +5,7 @@
 // With so few rows the pass is a matrix-vector product per page: 2 FLOP per K byte (e4m3), far
 // below what keeps a tensor-core pipeline fed, and every page's result is independent of every
 // other page's.  So there is no pipeline to synchronise at all: one warp owns one 128-key page
-// at a time, streams it with 16-byte loads (eight in flight per lane, 32 resident warps per SM),
+// at a time, streams it with 16-byte loads (sixteen in flight per lane, up to 24 resident warps per SM),
 // multiplies on the FMA pipe with fp32 accumulation (fma.rn.f32.f16 / .bf16: no conversion of
 // the products, e4m3 is widened to f16 exactly), reduces the lanes that share a key with
 // shuffles and keeps a running max.  The page table entry is the only dependent load.
@@ -53,14 +53,15 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
 }
 
 // F8: e4m3 cache (q e4m3 or bf16, multiplied as f16); otherwise bf16 cache and bf16 q.
+constexpr int kCtasPerSm = 3;                    // register budget: 85 per thread
 template <bool F8, int R>
-__global__ void __launch_bounds__(NWARPS * 32, 4)
+__global__ void __launch_bounds__(NWARPS * 32, kCtasPerSm)
 score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
   constexpr int QW = F8 ? 8 : 4;                 // 32-bit words of q per lane per row
   constexpr int L = F8 ? 8 : 16;                 // lanes that share one key
   constexpr int KPL = 32 / L;                    // keys per warp-wide load
   constexpr int NLOAD = BN / KPL;                // loads per lane per tile
-  constexpr int UNROLL = R == 4 ? 4 : 8;         // 16-byte loads in flight per lane
+  constexpr int UNROLL = R == 4 ? 8 : 16;        // 16-byte loads in flight per lane
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const MsaWorkItem w = p.work[blockIdx.y];
   const int b = w.batch, head0 = w.head0;
@@ -188,8 +189,9 @@ int score_gemv_launch(const MsaFmhaParams& p, cudaStream_t stream) {
     cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
     if (dev < 16) sms[dev] = nsm;
   }
-  // about 32 warps per SM over the whole grid, never more warps per item than it has tiles
-  const int want = (nsm * 32 + p.num_work * NWARPS - 1) / (p.num_work * NWARPS);
+  // the whole grid resident at once (a second, partial wave costs more than idle warp slots), never
+  // more warps per item than it has tiles
+  const int want = (nsm * kCtasPerSm) / p.num_work;
   const int cap = (p.max_k_tiles + NWARPS - 1) / NWARPS;
   const int chunks = std::max(1, std::min(want, cap));
   const dim3 grid(chunks, p.num_work);

@@ -156,80 +156,83 @@ topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
 }
 
 // Few rows (decode): one CTA per (token, head) row, its 256 threads share the row's pages, NK
-// per thread, kept in registers as order keys.  TOPK rounds: every thread offers its best key
-// below the previous winner, warps reduce with redux.sync, the CTA through shared memory.  The
-// order is the same strict total order (key desc, page asc), so the result is identical to the
+// per thread, kept in registers as order keys.  Two levels of the same selection loop, neither
+// with a CTA-wide barrier inside: every warp extracts its own TOPK best (each round the lanes offer
+// their best key below the previous winner, redux.sync picks the winner, lane r keeps winner r),
+// the 8 x TOPK survivors go through shared memory, and warp 0 extracts the final TOPK from them.
+// The order is the same strict total order (key desc, page asc), so the result is identical to the
 // thread-per-row kernel above.
+template <int NKEYS>
+__device__ __forceinline__ void warp_select_round(const uint32_t (&ord)[NKEYS], const uint32_t (&page)[NKEYS],
+                                                  uint32_t& last_ord, uint32_t& last_page, uint32_t& win_ord,
+                                                  uint32_t& win_page) {
+  uint32_t bo = 0u, bp = 0xffffffffu;
+#pragma unroll
+  for (int i = 0; i < NKEYS; ++i) {
+    // below the previous winner in (key desc, page asc) order; last_page starts at "before page 0"
+    const bool below = ord[i] < last_ord || (ord[i] == last_ord && static_cast<int32_t>(page[i]) > static_cast<int32_t>(last_page));
+    const bool better = ord[i] > bo || (ord[i] == bo && page[i] < bp);
+    if (below && ord[i] != 0u && better) { bo = ord[i]; bp = page[i]; }
+  }
+  win_ord = __reduce_max_sync(0xffffffffu, bo);
+  win_page = __reduce_min_sync(0xffffffffu, (bo == win_ord && bo != 0u) ? bp : 0xffffffffu);
+  if (win_ord != 0u) { last_ord = win_ord; last_page = win_page; }
+  else { last_ord = 0u; last_page = 0x7fffffffu; }            // nothing left: later rounds find nothing either
+}
+
 template <int TOPK, int NK, typename T>
 __global__ void __launch_bounds__(256)
 topk_row_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles, int total_q,
                 int nvp, int force_begin, int force_end_start) {
-  __shared__ uint32_t s_ord[2][8], s_page[2][8];
+  static_assert(TOPK <= 32, "one winner per lane");
+  __shared__ uint32_t s_ord[8 * TOPK], s_page[8 * TOPK];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t = blockIdx.x % total_q, head = blockIdx.x / total_q;
   const T* base = scores + static_cast<size_t>(head) * max_k_tiles * total_q + t;
-  uint32_t ord[NK];
+  uint32_t ord[NK], page[NK];
 #pragma unroll
   for (int i = 0; i < NK; ++i) {
-    const int page = tid + 256 * i;
+    const int pg = tid + 256 * i;
+    page[i] = static_cast<uint32_t>(pg);
     ord[i] = 0u;                                             // 0: not a candidate
-    if (page < nvp) {
-      const bool forced = page < force_begin || page >= force_end_start;
-      ord[i] = forced ? kForcedOrd : ord_key(static_cast<float>(base[static_cast<size_t>(page) * total_q]));
+    if (pg < nvp) {
+      const bool forced = pg < force_begin || pg >= force_end_start;
+      ord[i] = forced ? kForcedOrd : ord_key(static_cast<float>(base[static_cast<size_t>(pg) * total_q]));
     }
   }
-  uint32_t last_ord = 0xffffffffu;
-  int last_page = -1;
-  uint32_t sel[TOPK];
+  // level 1: this warp's TOPK best, winner r in lane r
+  uint32_t last_ord = 0xffffffffu, last_page = 0xffffffffu;   // (int32) -1: before page 0
+  uint32_t my_ord = 0u, my_page = 0xffffffffu;
 #pragma unroll
   for (int r = 0; r < TOPK; ++r) {
-    uint32_t bo = 0u, bp = 0xffffffffu;
-#pragma unroll
-    for (int i = 0; i < NK; ++i) {                           // pages ascend with i: strict > keeps the lowest page of a tie
-      const int page = tid + 256 * i;
-      const bool below = ord[i] < last_ord || (ord[i] == last_ord && page > last_page);
-      if (below && ord[i] > bo) { bo = ord[i]; bp = static_cast<uint32_t>(page); }
-    }
-    const uint32_t wo = __reduce_max_sync(0xffffffffu, bo);
-    const uint32_t wp = __reduce_min_sync(0xffffffffu, (bo == wo && bo != 0u) ? bp : 0xffffffffu);
-    if (lane == 0) { s_ord[r & 1][warp] = wo; s_page[r & 1][warp] = wp; }
-    __syncthreads();
-    uint32_t go = 0u, gp = 0xffffffffu;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      const uint32_t o = s_ord[r & 1][w], pg = s_page[r & 1][w];
-      if (o > go || (o == go && pg < gp)) { go = o; gp = pg; }
-    }
-    sel[r] = go != 0u ? gp : 0xffffffffu;
-    if (go != 0u) { last_ord = go; last_page = static_cast<int>(gp); }
-    else { last_ord = 0u; last_page = 0x7fffffff; }          // nothing left: later rounds find nothing either
+    uint32_t wo, wp;
+    warp_select_round<NK>(ord, page, last_ord, last_page, wo, wp);
+    if (lane == r) { my_ord = wo; my_page = wp; }
   }
-  if (tid != 0) return;
-  // ascending page order, -1 (0xffffffff) last
+  if (lane < TOPK) { s_ord[warp * TOPK + lane] = my_ord; s_page[warp * TOPK + lane] = my_page; }
+  __syncthreads();
+  if (warp != 0) return;
+  // level 2: the final TOPK among the 8 * TOPK survivors
+  constexpr int NC = 8 * TOPK / 32;
+  uint32_t cord[NC], cpage[NC];
 #pragma unroll
-  for (int k = 2; k <= TOPK; k <<= 1) {
+  for (int i = 0; i < NC; ++i) { cord[i] = s_ord[lane + 32 * i]; cpage[i] = s_page[lane + 32 * i]; }
+  last_ord = 0xffffffffu; last_page = 0xffffffffu;
+  uint32_t sel = 0xffffffffu;                                 // lane r: the r-th best page, or -1
 #pragma unroll
-    for (int j = k >> 1; j > 0; j >>= 1) {
-#pragma unroll
-      for (int i = 0; i < TOPK; ++i) {
-        const int l = i ^ j;
-        if (l > i) {
-          const uint32_t a = sel[i], b = sel[l];
-          const bool up = (i & k) == 0;
-          sel[i] = up ? min(a, b) : max(a, b);
-          sel[l] = up ? max(a, b) : min(a, b);
-        }
-      }
-    }
+  for (int r = 0; r < TOPK; ++r) {
+    uint32_t wo, wp;
+    warp_select_round<NC>(cord, cpage, last_ord, last_page, wo, wp);
+    if (lane == r) sel = wo != 0u ? wp : 0xffffffffu;
   }
-  int32_t* dst = out + (static_cast<size_t>(t) * num_heads + head) * TOPK;
+  // ascending page order, -1 (0xffffffff) last: rank = number of smaller entries (ties by lane)
+  int rank = 0;
 #pragma unroll
-  for (int i = 0; i < TOPK; i += 4) {
-    int4 v;
-    v.x = static_cast<int32_t>(sel[i]); v.y = static_cast<int32_t>(sel[i + 1]);
-    v.z = static_cast<int32_t>(sel[i + 2]); v.w = static_cast<int32_t>(sel[i + 3]);
-    *reinterpret_cast<int4*>(dst + i) = v;
+  for (int j = 0; j < TOPK; ++j) {
+    const uint32_t o = __shfl_sync(0xffffffffu, sel, j);
+    rank += (o < sel || (o == sel && j < lane)) ? 1 : 0;
   }
+  if (lane < TOPK) out[(static_cast<size_t>(t) * num_heads + head) * TOPK + rank] = static_cast<int32_t>(sel);
 }
 
 template <int TOPK>
@@ -251,7 +254,9 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
   }
   const int fe_start = fe <= nvp ? nvp - fe : 0;
   if (rows <= 2048 && nvp <= 256 * 32) {                     // decode-sized: a CTA per row
-    if (nvp <= 256 * 8)
+    if (nvp <= 256 * 4)
+      topk_row_kernel<TOPK, 4, T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
+    else if (nvp <= 256 * 8)
       topk_row_kernel<TOPK, 8, T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
     else
       topk_row_kernel<TOPK, 32, T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
