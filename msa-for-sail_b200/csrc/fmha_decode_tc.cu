@@ -1,7 +1,7 @@
 // Decode / short-query attention on tcgen05, sized for HBM bandwidth.
 //
 // Serves the q_len * (Hq/Hkv) <= 128 shapes of `fmha_sail` over a bf16 or e4m3 paged cache with
-// 128-key pages (e4m3: kind::f8f6f4 MMAs, Q and P converted to e4m3, P offset by 2^8): dense paged decode with split-KV (upstream dense mainloop + pack-GQA,
+// 128-key pages (e4m3: kind::f8f6f4 MMAs, Q and P converted to e4m3, P offset by 2^4): dense paged decode with split-KV (upstream dense mainloop + pack-GQA,
 // csrc/include/sm80_fmha_fwd_mainloop.hpp:262-636, api.py:308-318) and per-token sparse decode
 // over kv_block_indexes (csrc/include/sm80_fmha_sparse_fwd_mainloop.hpp:249-601).
 //
@@ -37,7 +37,7 @@ constexpr int BM = 128, BN = 128;
 constexpr int SUB_BYTES = BM * 128;             // one [128 rows][128 bytes] swizzled sub-tile
 constexpr int NTHREADS = 192;
 constexpr int PRODUCER_WARP = 4, MMA_WARP = 5;
-constexpr int MAX_SPARSE_TILES = 64;
+constexpr int MAX_SPARSE_TILES = 64;            // selected pages per work item
 constexpr int MAX_STAGES = 6;
 constexpr int QUAD_MAX_ROWS = 16;               // rows of a work item the 4-way column split accepts
 constexpr int STAGE_LD = kHeadDim + 4;          // floats per staged O row (padding spreads the banks)
@@ -61,15 +61,18 @@ __device__ __forceinline__ unsigned long long global_ns() {
 //         work on a tile instead of the first lanes of one; the four partial (O, m, l) of a row
 //         are combined in shared memory at the end.
 //   F8 && QUAD ("dual"): half the shared memory and 256 TMEM columns, two CTAs per SM, so the
-//         prologue and epilogue of short work items overlap with another item's loads.  The
-//         barriers live in rows 16-31 of the Q tile, which no real row uses.
+//         prologue and epilogue of short work items overlap with another item's loads.  Tiles are
+//         half pages (64 keys): two 64-column S buffers and O fit the 256 columns, so Q K^T of tile
+//         j + 1 still overlaps the softmax of tile j.  The barriers live in rows 16-31 of the Q
+//         tile, which no real row uses.
 template <bool F8, bool QUAD>
 struct Cfg {
   static constexpr bool DUAL = F8 && QUAD;
-  static constexpr int NSUB = F8 ? 1 : 2;                 // 128-byte-wide sub-tiles per 128 x 128 tile
-  static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
+  static constexpr int TK = DUAL ? 64 : 128;              // keys per tile
+  static constexpr int NSUB = F8 ? 1 : 2;                 // 128-byte-wide sub-tiles per tile
+  static constexpr int TILE_BYTES = NSUB * TK * 128;
   static constexpr int RING_BYTES = DUAL ? 48 * 1024 : 96 * 1024;
-  static constexpr int STAGES = RING_BYTES / TILE_BYTES;  // bf16 3, e4m3 6 (dual: 3)
+  static constexpr int STAGES = RING_BYTES / TILE_BYTES;  // bf16 3, e4m3 6 (dual: 6 half pages)
   static constexpr int OFF_Q = 0;
   // dual: rows 112-127 of the Q tile are never real rows, the K ring may start there
   static constexpr int OFF_K = DUAL ? SUB_BYTES - 2048 : 2 * SUB_BYTES;
@@ -77,9 +80,9 @@ struct Cfg {
   static constexpr int END = OFF_V + RING_BYTES;
   static constexpr int OFF_BAR = DUAL ? 2048 : END;
   static constexpr int SMEM_BYTES = (DUAL ? END : END + 1024) + 1024;   // + slack to align the base to 1 KB
-  static constexpr int NBUF = DUAL ? 1 : 2;               // S buffers in TMEM
+  static constexpr int NBUF = 2;                          // S buffers in TMEM
   static constexpr int TMEM_COLS = DUAL ? 256 : 512;
-  static constexpr int O_COL = NBUF * BN;
+  static constexpr int O_COL = NBUF * TK;
   static constexpr int MIN_CTAS = DUAL ? 2 : 1;
   static_assert(STAGES <= MAX_STAGES, "barrier table");
   static_assert(4 * QUAD_MAX_ROWS * STAGE_LD * 4 <= RING_BYTES, "O staging fits the K ring");
@@ -90,7 +93,8 @@ __global__ void __launch_bounds__(NTHREADS, (Cfg<F8, QUAD>::MIN_CTAS))
 decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
   using C = Cfg<F8, QUAD>;
-  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STAGES = C::STAGES, NBUF = C::NBUF;
+  constexpr int NSUB = C::NSUB, TILE_BYTES = C::TILE_BYTES, STAGES = C::STAGES, NBUF = C::NBUF, TK = C::TK;
+  constexpr int UPP = BN / TK;                      // tiles per page
   constexpr int OFF_Q = C::OFF_Q, OFF_K = C::OFF_K, OFF_V = C::OFF_V, OFF_BAR = C::OFF_BAR;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -98,17 +102,19 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const uint32_t bars = smem_base + OFF_BAR;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
-  int* s_tiles = reinterpret_cast<int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 16);      // sparse: valid pages, in order
-  int* s_phys = s_tiles + MAX_SPARSE_TILES;                                            // ... and their physical ids
-  int* s_ntiles = s_phys + MAX_SPARSE_TILES;
+  int* s_tiles = reinterpret_cast<int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 16);      // sparse: first key / TK of every tile, in order
+  int* s_phys = s_tiles + MAX_SPARSE_TILES * UPP;                                      // ... and the physical id of its page
+  int* s_ntiles = s_phys + MAX_SPARSE_TILES * UPP;
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
   constexpr int SUB_ELEMS = F8 ? 128 : 64;          // elements of head_dim per sub-tile
   constexpr int KSTEPS = F8 ? 4 : 8;                // MMAs per 128-deep contraction
-  // e4m3 P has 3 mantissa bits: keep it in (2^-6, 2^8] by using the exact running max (no lazy
-  // rescale) and a 2^8 offset, the same trick as the upstream e4m3 path
-  // (csrc/include/fmha_common.hpp:567-570)
-  constexpr float kRescaleThreshold = F8 ? 0.0f : 8.0f;
-  constexpr float kPOffset = F8 ? 8.0f : 0.0f;
+  // e4m3 P (3 mantissa bits, largest finite value 448): written as 2^(x - m + 4) with m the running
+  // max, which is raised (and O rescaled) only when it lags the true max by more than 4: P stays
+  // within (0, 2^8], and what falls below e4m3's smallest subnormal (2^-9) is a weight under 2^-13
+  // of the row's largest.  (Upstream uses the exact max and a 2^8 offset, fmha_common.hpp:567-570;
+  // with the exact max nearly every tile of a short work item triggers an O rescale.)
+  constexpr float kRescaleThreshold = F8 ? 4.0f : 8.0f;
+  constexpr float kPOffset = F8 ? 4.0f : 0.0f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned long long* trace = (threadIdx.x == 0 && g_trace) ? g_trace + 16ull * blockIdx.x : nullptr;
   const long long clk0 = clock64();
@@ -173,15 +179,30 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       for (int j0 = tb; j0 < te; j0 += 32) {
         const int j = j0 + lane;
         const int blk = j0 == tb ? blk_first : (j < te ? blocks[j] : -1);
-        const bool ok = blk >= 0 && blk * BN < kv_len && blk * BN <= i_base + off;
-        const unsigned m = __ballot_sync(0xffffffffu, ok);
-        const int pos = n + __popc(m & ((1u << lane) - 1u));
-        if (ok && pos < MAX_SPARSE_TILES) { s_tiles[pos] = blk; s_phys[pos] = p.kv_indices[page_base + blk]; }
-        n += __popc(m);
+        // tiles of this page that hold a key this token may see
+        int nu = 0;
+        if (blk >= 0) {
+          const int vis = min(kv_len, i_base + off + 1) - blk * BN;          // visible keys from the page start on
+          nu = vis <= 0 ? 0 : min(UPP, (vis + TK - 1) / TK);
+        }
+        int incl = nu;                                         // inclusive scan over the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += v;
+        }
+        const int pos = n + incl - nu;
+        if (nu > 0 && pos + nu <= MAX_SPARSE_TILES * UPP) {
+          const int ph = p.kv_indices[page_base + blk];
+          for (int u = 0; u < nu; ++u) { s_tiles[pos + u] = blk * UPP + u; s_phys[pos + u] = ph; }
+        }
+        n += __shfl_sync(0xffffffffu, incl, 31);
       }
-      if (lane == 0) *s_ntiles = min(n, MAX_SPARSE_TILES);
+      if (lane == 0) *s_ntiles = min(n, MAX_SPARSE_TILES * UPP);
     } else if (lane == 0) {
-      *s_ntiles = max(0, te - tb);
+      // [tb, te) pages of the sequence, up to the last tile that holds a key
+      const int keys = min(te * BN, kv_len) - tb * BN;
+      *s_ntiles = keys <= 0 ? 0 : (keys + TK - 1) / TK;
     }
   }
   if (warp == MMA_WARP) {
@@ -194,7 +215,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const uint32_t tmem = *tmem_slot;
   const int n_tiles = *s_ntiles;
   if (trace) trace[3] = clock64() - clk0;
-  auto tile_page = [&](int j) -> int { return sparse ? s_tiles[j] : tb + j; };     // logical page of tile j
+  auto tile_key0 = [&](int j) -> int { return (sparse ? s_tiles[j] : tb * UPP + j) * TK; };   // position of the first key of tile j
 
   const bool run = *abort_flag == 0;
   if (!run) {
@@ -214,32 +235,35 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       }
       __syncwarp();
     }
-    // page-table entries: one per lane, 32 tiles at a time, the next batch already in flight
+    // page-table entries: one per lane, 32 pages at a time, the next batch already in flight
     int phys_cur = 0, phys_next = 0;
+    const int n_pages = (n_tiles + UPP - 1) / UPP;
     if (!sparse) {
-      phys_cur = lane < n_tiles ? p.kv_indices[page_base + tb + lane] : 0;
-      phys_next = 32 + lane < n_tiles ? p.kv_indices[page_base + tb + 32 + lane] : 0;
+      phys_cur = lane < n_pages ? p.kv_indices[page_base + tb + lane] : 0;
+      phys_next = 32 + lane < n_pages ? p.kv_indices[page_base + tb + 32 + lane] : 0;
     }
     uint32_t fix_phase = 0;
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int st = j % STAGES;
-      const int lp = tile_page(j);
-      if (!sparse && j > 0 && (j & 31) == 0) {
+      const int key0 = tile_key0(j);
+      const int row_in_page = key0 % BN;
+      const int pg = j / UPP;                                // dense: page index within this item
+      if (!sparse && j > 0 && (j % (32 * UPP)) == 0) {
         phys_cur = phys_next;
-        phys_next = j + 32 + lane < n_tiles ? p.kv_indices[page_base + tb + j + 32 + lane] : 0;
+        phys_next = pg + 32 + lane < n_pages ? p.kv_indices[page_base + tb + pg + 32 + lane] : 0;
       }
-      const int phys = sparse ? s_phys[j] : __shfl_sync(0xffffffffu, phys_cur, j & 31);
-      const int valid_rows = min(BN, kv_len - lp * BN);
-      const bool fix = valid_rows < BN;
+      const int phys = sparse ? s_phys[j] : __shfl_sync(0xffffffffu, phys_cur, pg & 31);
+      const int valid_rows = min(TK, kv_len - key0);
+      const bool fix = valid_rows < TK;
       alive = mbar_wait(bar(K_EMPTY + st), ((j / STAGES) & 1) ^ 1, abort_flag);
       if (!alive) break;
       if (elect_one()) {
         mbar_arrive_expect_tx(bar(K_FULL + st), TILE_BYTES);
 #pragma unroll
         for (int hlf = 0; hlf < NSUB; ++hlf)
-          tma_load_4d(smem_base + OFF_K + st * TILE_BYTES + hlf * SUB_BYTES, &tm_k, bar(K_FULL + st), hlf * SUB_ELEMS, 0,
-                      kvh, phys);
+          tma_load_4d(smem_base + OFF_K + st * TILE_BYTES + hlf * SUB_BYTES, &tm_k, bar(K_FULL + st), hlf * SUB_ELEMS,
+                      row_in_page, kvh, phys);
       }
       __syncwarp();
       if (!has_o) continue;
@@ -250,7 +274,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         mbar_arrive_expect_tx(vbar, TILE_BYTES);
 #pragma unroll
         for (int hlf = 0; hlf < NSUB; ++hlf)
-          tma_load_4d(smem_base + OFF_V + st * TILE_BYTES + hlf * SUB_BYTES, &tm_v, vbar, hlf * SUB_ELEMS, 0, kvh, phys);
+          tma_load_4d(smem_base + OFF_V + st * TILE_BYTES + hlf * SUB_BYTES, &tm_v, vbar, hlf * SUB_ELEMS, row_in_page, kvh, phys);
       }
       __syncwarp();
       if (fix) {                                             // rows past kv_len must read as 0 in V
@@ -259,7 +283,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         fix_phase ^= 1;
         if (alive) {
           unsigned char* vt = smem_gen + OFF_V + st * TILE_BYTES;
-          for (int c = lane; c < (BN - valid_rows) * 8 * NSUB; c += 32) {
+          for (int c = lane; c < (TK - valid_rows) * 8 * NSUB; c += 32) {
             const int r = valid_rows + c / (8 * NSUB), ch = c % (8 * NSUB);
             *reinterpret_cast<uint4*>(vt + (ch >> 3) * SUB_BYTES + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
           }
@@ -271,12 +295,14 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     }
   } else if (warp == MMA_WARP) {
     // =========================== MMA issuer ===========================
-    constexpr uint32_t IDESC_QK = F8 ? idesc_e4m3(BM, BN, false, false) : idesc_bf16(BM, BN, false, false);
+    constexpr uint32_t IDESC_QK = F8 ? idesc_e4m3(BM, TK, false, false) : idesc_bf16(BM, TK, false, false);
     constexpr uint32_t IDESC_PV = F8 ? idesc_e4m3(BM, kHeadDim, false, true) : idesc_bf16(BM, kHeadDim, false, true);
     const uint64_t dk_hi = smem_desc(0, 16, 1024) & 0xFFFFFFFFFFFF0000ull;
     const uint64_t dv_hi = smem_desc(0, SUB_BYTES, 1024) & 0xFFFFFFFFFFFF0000ull;
-    constexpr int V_KSTEP = (BN / KSTEPS) * 128;     // bytes between the key slices of consecutive P.V MMAs
-    auto sbuf = [&](int j) -> uint32_t { return tmem + (j % NBUF) * BN; };
+    constexpr int KEYS_PER_PV = F8 ? 32 : 16;        // keys one P.V MMA contracts over
+    constexpr int PV_STEPS = TK / KEYS_PER_PV;
+    constexpr int V_KSTEP = KEYS_PER_PV * 128;       // bytes between the key slices of consecutive P.V MMAs
+    auto sbuf = [&](int j) -> uint32_t { return tmem + (j % NBUF) * TK; };
     auto issue_qk = [&](int j) {
       const uint32_t qa = (smem_base + OFF_Q) >> 4, ka = (smem_base + OFF_K + (j % STAGES) * TILE_BYTES) >> 4;
 #pragma unroll
@@ -289,7 +315,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     auto issue_pv = [&](int j) {
       const uint32_t va = (smem_base + OFF_V + (j % STAGES) * TILE_BYTES) >> 4;
 #pragma unroll
-      for (int k = 0; k < KSTEPS; ++k) {                // P: 8 TMEM columns per MMA in both formats
+      for (int k = 0; k < PV_STEPS; ++k) {              // P: 8 TMEM columns per MMA in both formats
         const uint64_t vd = dv_hi | ((va + k * (V_KSTEP >> 4)) & 0x3FFF);
         if constexpr (F8) mma_ts_f8(tmem + C::O_COL, sbuf(j) + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
         else mma_ts(tmem + C::O_COL, sbuf(j) + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
@@ -391,23 +417,27 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     if constexpr (QUAD) {
       // quadrant `warp` owns key columns [32 warp, 32 warp + 32) of every tile
       for (int j = 0; j < n_tiles && alive; ++j) {
-        const uint32_t tS = tmem + (j % NBUF) * BN + lane_addr;
+        const uint32_t tS = tmem + (j % NBUF) * TK + lane_addr;
         alive = mbar_wait(bar(S_FULL + j % NBUF), (j / NBUF) & 1, abort_flag);
         if (!alive) break;
-        if (trace && j < 4) trace[4 + j] = clock64() - clk0;
+        if (trace && j == 12) trace[4] = clock64() - clk0;       // S of tile 12 ready
+        if (trace && j == 13) trace[14] = clock64() - clk0;
         tc_fence_after();
-        const int pos0 = tile_page(j) * BN + warp * 32;
-        uint32_t sv[32];
-        tmem_ld32(tS + warp * 32, sv);
+        constexpr int CW = TK / 4;                           // key columns of a tile per quadrant
+        const int pos0 = tile_key0(j) + warp * CW;
+        uint32_t sv[CW];
+        if constexpr (CW == 32) tmem_ld32(tS + warp * CW, sv);
+        else tmem_ld16(tS + warp * CW, sv);
         tmem_wait_ld();
-        if (pos0 + 31 > lim) {
+        if (trace && j == 12) trace[5] = clock64() - clk0;       // ... loaded
+        if (pos0 + CW - 1 > lim) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
+          for (int e = 0; e < CW; ++e)
             if (pos0 + e > lim) sv[e] = 0xff800000u;
         }
         float mxs[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int e = 0; e < 32; e += 2)
+        for (int e = 0; e < CW; e += 2)
           mxs[(e >> 1) & 1] = max3(mxs[(e >> 1) & 1], __uint_as_float(sv[e]), __uint_as_float(sv[e + 1]));
         const float mx = fmaxf(mxs[0], mxs[1]);
         const float m_cand = fmaxf(m_used, mx * scale_log2);
@@ -430,13 +460,12 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         }
         const float msafe = ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset;
         float l0 = 0.f, l1 = 0.f;
-        constexpr int PCOLS = F8 ? 8 : 16;                   // TMEM columns of P per 32 keys
-        uint32_t pk[PCOLS], zero[PCOLS];
-#pragma unroll
-        for (int e = 0; e < PCOLS; ++e) zero[e] = 0u;
+        if (trace && j == 12) trace[6] = clock64() - clk0;       // ... max / rescale done
+        constexpr int PCOLS = F8 ? CW / 4 : CW / 2;          // TMEM columns of this quadrant's P
+        uint32_t pk[PCOLS];
         if constexpr (F8) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
+          for (int e = 0; e < CW; e += 4) {
             const float p0 = exp2_fast(fmaf(__uint_as_float(sv[e]), scale_log2, -msafe));
             const float p1 = exp2_fast(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -msafe));
             const float p2 = exp2_fast(fmaf(__uint_as_float(sv[e + 2]), scale_log2, -msafe));
@@ -448,32 +477,44 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
+          for (int e = 0; e < CW; e += 2) {
             const float p0 = exp2_fast(fmaf(__uint_as_float(sv[e]), scale_log2, -msafe));
             const float p1 = exp2_fast(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -msafe));
             l0 += p0; l1 += p1;
             pk[e >> 1] = pack2<false>(p0, p1);
           }
         }
-        // P of this quadrant's rows: own 32 keys, zero for the other 96
+        // P of this quadrant's rows: own keys, zero for the other three quarters of the tile
+        if constexpr (PCOLS == 4) {                           // 16 columns in all: one store
+          uint32_t all[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if constexpr (F8) { if (q == warp) tmem_st8(tS + q * PCOLS, pk); else tmem_st8(tS + q * PCOLS, zero); }
-          else { if (q == warp) tmem_st16(tS + q * PCOLS, pk); else tmem_st16(tS + q * PCOLS, zero); }
+          for (int c = 0; c < 16; ++c) all[c] = (c >> 2) == warp ? pk[c & 3] : 0u;
+          tmem_st16(tS, all);
+        } else {
+          uint32_t zero[PCOLS];
+#pragma unroll
+          for (int e = 0; e < PCOLS; ++e) zero[e] = 0u;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if constexpr (PCOLS == 8) { if (q == warp) tmem_st8(tS + q * PCOLS, pk); else tmem_st8(tS + q * PCOLS, zero); }
+            else { if (q == warp) tmem_st16(tS + q * PCOLS, pk); else tmem_st16(tS + q * PCOLS, zero); }
+          }
         }
         l_sum += l0 + l1;
+        if (trace && j == 12) trace[7] = clock64() - clk0;       // ... P stored (before the wait)
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_FULL + j % NBUF));
+        if (trace && j == 12) trace[15] = clock64() - clk0;      // ... P_FULL arrived
         if (trace && j == n_tiles - 1) trace[8] = clock64() - clk0;
       }
     } else {
     for (int j = 0; j < n_tiles && alive; ++j) {
-      const uint32_t tS = tmem + (j % NBUF) * BN + lane_addr;
+      const uint32_t tS = tmem + (j % NBUF) * TK + lane_addr;
       alive = mbar_wait(bar(S_FULL + j % NBUF), (j / NBUF) & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
-      const int pos0 = tile_page(j) * BN;
+      const int pos0 = tile_key0(j);
       uint32_t sv[4][32];
       tmem_ld32(tS, sv[0]);
       tmem_ld32(tS + 32, sv[1]);
@@ -733,6 +774,8 @@ int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   if (grid64 > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   CUtensorMap tq, tk, tv;
   const uint64_t e = f8 ? 1 : 2;
+  // the 4-way column split needs O (its quadrants do not share a row max) and <= 16 rows
+  const bool quad = has_o && p.decode_rows <= QUAD_MAX_ROWS;
   {
     const uint64_t kd[4] = {128, BN, static_cast<uint64_t>(p.num_kv_heads), static_cast<uint64_t>(p.kv_extent)};
     const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * e, static_cast<uint64_t>(p.k_stride_head) * e,
@@ -741,7 +784,7 @@ int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
                             static_cast<uint64_t>(p.v_stride_page) * e};
     const void* vptr = has_o ? p.v : p.k;
     if (f8) {
-      const uint32_t kbox[4] = {128, BN, 1, 1};
+      const uint32_t kbox[4] = {128, static_cast<uint32_t>(quad ? Cfg<true, true>::TK : BN), 1, 1};   // dual: half pages
       if (make_tma_map_u8(&tk, p.k, 4, kd, ks, kbox) != MSA_OK ||
           make_tma_map_u8(&tv, vptr, 4, kd, has_o ? vs : ks, kbox) != MSA_OK)
         return MSA_ERR_LAUNCH;
@@ -757,8 +800,6 @@ int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
         return MSA_ERR_LAUNCH;
     }
   }
-  // the 4-way column split needs O (its quadrants do not share a row max) and <= 16 rows
-  const bool quad = has_o && p.decode_rows <= QUAD_MAX_ROWS;
   static bool attr_done[16][4] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -814,8 +855,8 @@ int fmha_decode_tc_occupancy(int f8, int quad) {
 extern "C" int msa_debug_decode_occupancy(int f8, int quad) { return msa::fmha_decode_tc_occupancy(f8, quad); }
 
 // diagnostic, not part of the documented ABI: device buffer of 16 x uint64 per CTA, or NULL to stop
-// [0] start ns  [1] end ns  [2] SM id; clocks since entry: [3] prologue done, [4..7] S of tiles 0-3
-// ready, [8] last P written, [9] last P.V done, [10] O staged, [11] staging barrier passed,
+// [0] start ns  [1] end ns  [2] SM id; clocks since entry: [3] prologue done, [4..7], [14], [15] steps of
+// tile 12 / 13 in the softmax (S ready, loaded, max done, P stored, S of 13 ready, P_FULL arrived), [8] last P written, [9] last P.V done, [10] O staged, [11] staging barrier passed,
 // [12] rows combined and stored, [13] exit
 extern "C" void msa_debug_decode_trace(unsigned long long* device_buf) {
   cudaMemcpyToSymbol(msa::decode_tc::g_trace, &device_buf, sizeof(device_buf));
