@@ -53,6 +53,8 @@ WORKLOADS = {
         "msa_decode", dict(b=32, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=True)),
     "msa_decode_bf16_b32_kv131072_h64kv8_top16_split4": (
         "msa_decode", dict(b=32, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=False)),
+    "msa_decode_e4m3_b8_kv131072_h64kv8_top16_split4": (
+        "msa_decode", dict(b=8, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=True)),                # small: ncu
     "paged_decode_b1_kv1048576_h64kv8": ("decode", dict(b=1, kl=1048576, hq=64, hk=8)),
     "paged_decode_b1_kv131072_h64kv8": ("decode", dict(b=1, kl=131072, hq=64, hk=8)),               # small: ncu
 }
@@ -62,12 +64,16 @@ DEFAULT = "paged_prefill_b4_s8192_h64kv8"
 # summarised under profiles/ (captured on the small variant and scaled by the units processed
 # where the full workload is too large to capture with --set full)
 TRAFFIC = {
-    "paged_prefill_b4_s8192_h64kv8": (0.90e9, "scaled x8.0 from the b2_s4096_h32kv4 capture (112 MB)"),
-    "paged_prefill_b2_s4096_h32kv4": (112.1e6, "captured"),
-    "paged_decode_b1_kv1048576_h64kv8": (4.33e9, "scaled x8 from the kv131072 capture (541.6 MB)"),
-    "paged_decode_b1_kv131072_h64kv8": (541.6e6, "captured"),
-    "msa_prefill_b1_s8192_h32kv4_top16": (1.015e9, "captured (sparse_tc_kernel; merge: 1.148e9)"),
-    "msa_prefill_b2_s32768_h64kv8_top16": (16.2e9, "scaled x16 from the b1_s8192_h32kv4 capture (sparse_tc_kernel)"),
+    "paged_prefill_b4_s8192_h64kv8": (0.89e9, "scaled x8.0 from the b2_s4096_h32kv4 capture (111.5 MB)"),
+    "paged_prefill_b2_s4096_h32kv4": (111.5e6, "captured"),
+    "paged_decode_b1_kv1048576_h64kv8": (4.33e9, "scaled x8 from the kv131072 capture (541.7 MB)"),
+    "paged_decode_b1_kv131072_h64kv8": (541.7e6, "captured"),
+    "msa_prefill_b1_s8192_h32kv4_top16": (1.056e9, "captured (sparse_tc_kernel; sparse_merge_kernel: 1.032e9)"),
+    "msa_prefill_b2_s32768_h64kv8_top16": (16.9e9, "scaled x16 from the b1_s8192_h32kv4 capture (sparse_tc_kernel; "
+                                                    "sparse_merge_kernel: 16.5e9)"),
+    "msa_decode_e4m3_b8_kv131072_h64kv8_top16_split4": (138.1e6, "captured (score_gemv_kernel; decode_tc_kernel: 33.9e6)"),
+    "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4": (552e6, "scaled x4 from the b8 capture (score_gemv_kernel; "
+                                                               "decode_tc_kernel: 135e6)"),
 }
 
 

@@ -102,6 +102,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const uint32_t bars = smem_base + OFF_BAR;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
+  volatile int* skip_flag = abort_flag + 1;      // set when the status word already reports a timeout
   int* s_tiles = reinterpret_cast<int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 16);      // sparse: first key / TK of every tile, in order
   int* s_phys = s_tiles + MAX_SPARSE_TILES * UPP;                                      // ... and the physical id of its page
   int* s_ntiles = s_phys + MAX_SPARSE_TILES * UPP;
@@ -158,6 +159,10 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const int page_base = p.kv_page_indptr[b];
   const int n_active_warps = QUAD ? 4 : (nrows + 31) / 32;
 
+  // a timeout reported earlier on this device (status word not cleared yet): do not start.  Read by
+  // another thread than the one that sets up the barriers, so the load overlaps that work.
+  if (threadIdx.x == blockDim.x - 1)
+    *skip_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
   if (threadIdx.x == 0) {
     mbar_init(bar(Q_FULL), F8 ? 32 * n_active_warps : 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -167,8 +172,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     for (int s = 0; s < NBUF; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 32 * n_active_warps); }
     mbar_init(bar(PV_DONE), 1);
     mbar_init(bar(V_FIX), 1);
-    // a timeout reported earlier on this device (status word not cleared yet): do not start
-    *abort_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
+    *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == PRODUCER_WARP) {
@@ -217,7 +221,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   if (trace) trace[3] = clock64() - clk0;
   auto tile_key0 = [&](int j) -> int { return (sparse ? s_tiles[j] : tb * UPP + j) * TK; };   // position of the first key of tile j
 
-  const bool run = *abort_flag == 0;
+  const bool run = *skip_flag == 0;
   if (!run) {
     // nothing: fall through to the teardown
   } else if (warp == PRODUCER_WARP) {

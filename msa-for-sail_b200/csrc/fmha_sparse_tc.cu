@@ -336,6 +336,7 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const uint32_t bars = smem_base + OFF_BAR;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
+  volatile int* skip_flag = abort_flag + 1;      // set when the status word already reports a timeout
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool tracing = static_cast<int>(blockIdx.x) == g_trace_cta;
@@ -360,14 +361,17 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const int pos0 = lpage * BN;
   const int valid_rows = min(BN, kv_len - pos0);
 
+  // a timeout reported earlier on this device (status word not cleared yet): do not start.  Read by
+  // another thread than the one that sets up the barriers, so the load overlaps that work.
+  if (threadIdx.x == blockDim.x - 1)
+    *skip_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
   if (threadIdx.x == 0) {
     mbar_init(bar(K_FULL), 1); mbar_init(bar(V_FULL), 1); mbar_init(bar(V_FIX), 1);
     for (int s = 0; s < 2; ++s) { mbar_init(bar(Q_FULL + s), 1);  mbar_init(bar(Q_EMPTY + s), 1); }
     for (int s = 0; s < NSBUF; ++s) { mbar_init(bar(S_FULL + s), 1);  mbar_init(bar(P_FULL + s), BM); }
     for (int s = 0; s < 4; ++s) mbar_init(bar(META_FULL + s), BM);
     mbar_init(bar(O_FULL), 1);  mbar_init(bar(O_FREE), 2 * BM);       // both epilogue warpgroups drain O
-    // a timeout reported earlier on this device (status word not cleared yet): do not start
-    *abort_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
+    *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == MMA_WARP) {
@@ -379,7 +383,7 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  const bool run = *abort_flag == 0;
+  const bool run = *skip_flag == 0;
   if (!run) {
     // nothing: fall through to the teardown
   } else if (warp >= GATHER_WARP0 && warp < GATHER_WARP0 + GATHER_WARPS) {

@@ -66,6 +66,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   const uint32_t bars = smem_base + OFF_BAR;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + OFF_BAR + NUM_BARS * 8 + 8);
+  volatile int* skip_flag = abort_flag + 1;      // set when the status word already reports a timeout
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -97,6 +98,10 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   }
   const int n_total = max(n_tiles[0], n_tiles[1]);
 
+  // a timeout reported earlier on this device (status word not cleared yet): do not start.  Read by
+  // another thread than the one that sets up the barriers, so the load overlaps that work.
+  if (threadIdx.x == blockDim.x - 1)
+    *skip_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
   if (threadIdx.x == 0) {
     mbar_init(bar(Q_FULL), 1);
     for (int s = 0; s < 2; ++s) {
@@ -106,8 +111,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       mbar_init(bar(O_FULL + s), 1);
     }
     mbar_init(bar(V_FIX), 1);
-    // a timeout reported earlier on this device (status word not cleared yet): do not start
-    *abort_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
+    *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == MMA_WARP) {
@@ -119,7 +123,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  const bool run = *abort_flag == 0;
+  const bool run = *skip_flag == 0;
   if (!run) {
     // nothing: fall through to the teardown
   } else if (warp == PRODUCER_WARP) {
