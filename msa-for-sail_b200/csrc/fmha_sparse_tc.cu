@@ -63,6 +63,9 @@ constexpr uint32_t O_COL = NSBUF * BN;
 enum Bar { K_FULL = 0, V_FULL = 1, V_FIX = 2, Q_FULL = 3, Q_EMPTY = 5, S_FULL = 7, P_FULL = 10, O_FULL = 13,
            O_FREE = 14, META_FULL = 15, NUM_BARS = 19 };
 
+// test hook: take the global-atomics index kernels even when the histogram fits shared memory
+bool g_force_global_index = false;
+
 // optional clock trace of one CTA (debugging aid): [6 roles][512 chunks][8 tags]; roles: softmax 0/1,
 // MMA 2, loaders 3, epilogue 4
 __device__ unsigned long long g_trace[6 * 512 * 8];
@@ -743,7 +746,7 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   const int tpc = BM / G;
   const int rows_per_item = tpc * ITEM_CHUNKS;
   const size_t hist_bytes = static_cast<size_t>(NP) * 4;
-  const bool smem_hist = hist_bytes <= 48 * 1024;
+  const bool smem_hist = hist_bytes <= 48 * 1024 && !g_force_global_index;
   const unsigned n_blk_s = static_cast<unsigned>((p.total_q + 255) / 256) * p.num_kv_heads;
   auto index_pass = [&](bool scatter) {
     if (!smem_hist) {
@@ -824,6 +827,9 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 }
 
 }  // namespace msa
+
+// Test hook (not part of the documented ABI): exercise the index kernels that large page counts use.
+extern "C" void msa_debug_sparse_force_global_index(int on) { msa::sparse_tc::g_force_global_index = on != 0; }
 
 // Debug aid: choose the CTA whose phase clocks are recorded (-1 = none) / read the record back.
 extern "C" void msa_debug_sparse_trace_cta(int cta) {
