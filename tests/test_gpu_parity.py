@@ -373,6 +373,9 @@ def test_sparse_golden(sparse_path):
     ([300, 77], [1500, 700], 8, 2, 8, 1, False),             # many tokens per page, tail pages
     ([200], [1100], 16, 1, 16, 1, False),                    # h_r = 16: 8 tokens per chunk
     ([500], [3000], 2, 2, 4, 1, False),                      # h_r = 1: 128 tokens per chunk
+    ([1, 1, 1], [3000, 129, 5000], 64, 8, 16, 4, True),      # e4m3 decode, 8 rows per item, -1 padded lists
+    ([1, 1, 1], [3000, 129, 5000], 64, 8, 16, 4, False),     # same on a bf16 cache
+    ([2, 1], [1000, 4100], 32, 2, 8, 1, True),               # e4m3, 16 rows per item, two tokens
 ])
 def test_sparse_matches_oracle(qo_lens, kv_lens, hq, hk, kbn, splits, fp8, sparse_path):
     api = _api()
