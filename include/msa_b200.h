@@ -167,6 +167,43 @@ int msa_plan_dense(const MsaPlanArgs* args, MsaWorkItem* work, int32_t capacity,
                    int32_t* splits_per_row /* [total_q] host */,
                    int32_t* max_splits_out);
 
+/* Planning on the device, for callers that capture plan + run into one CUDA graph and only
+ * update the length tensors between replays (upstream: `graph_safe=True`, the
+ * prepare_plan_metadata + plan kernels, api.py:916-941, 1040-1048, 1196-1203).
+ * Everything that sizes a launch is fixed when the graph is built: batch, the row tile
+ * (one tile of block_m rows per batch item: qo_len * pack <= block_m), the split count.
+ * One kernel launch on `stream`; reads no device memory on the host, allocates nothing.
+ * Fills, for i in [0, batch):  qo_start / kv_start (exclusive prefix sums, [batch + 1]),
+ * kv_len_out, qo_offset_out (causal: kv_len - qo_len where qo_offset_in is NULL or
+ * negative; non-causal: `noncausal_offset`), kv_page_indptr ([batch + 1], pages of
+ * `page_size` keys, NULL for ragged K/V), token_batch ([max_total_q], NULL when unused),
+ * splits_per_row ([max_total_q], = num_splits) and the work list: exactly
+ * batch * (num_qo_heads / pack) * num_splits items, item ((b * groups) + g) * S + s
+ * covering the s-th of S equal chunks of the key tiles batch item b can see (empty range
+ * when it has fewer tiles).  NULL outputs are skipped. */
+typedef struct MsaPlanDeviceArgs {
+  const int32_t* qo_len;       /* [B] device */
+  const int32_t* kv_len;       /* [B] device */
+  const int32_t* qo_offset_in; /* [B] device or NULL */
+  int32_t* qo_start;
+  int32_t* kv_start;
+  int32_t* kv_len_out;
+  int32_t* qo_offset_out;
+  int32_t* kv_page_indptr;
+  int32_t* token_batch;
+  int32_t* splits_per_row;
+  MsaWorkItem* work;
+  int32_t batch;
+  int32_t num_qo_heads, num_kv_heads;
+  int32_t block_m, pack, num_splits;
+  int32_t page_size;           /* <= 0: ragged */
+  int32_t causal;
+  int32_t noncausal_offset;
+  int32_t max_total_q;
+  int32_t reserved;
+} MsaPlanDeviceArgs;
+int msa_plan_device(const MsaPlanDeviceArgs* args, msa_stream_t stream);
+
 /* Split-KV forward + merge with the partial-result scratch held inside the library.
  * No counterpart in the upstream project (there the caller always owns the split
  * workspace, api.py:141-167).  It exists for embedders that may not allocate device
@@ -194,7 +231,7 @@ const char* msa_status_string(int code);
 int msa_build_arch(void);
 
 /* sizeof() of the ABI structs as the library was compiled: 0 = MsaFmhaParams,
- * 1 = MsaWorkItem, 2 = MsaPlanArgs.  Lets a foreign-language binding verify its
+ * 1 = MsaWorkItem, 2 = MsaPlanArgs, 3 = MsaPlanDeviceArgs.  Lets a foreign-language binding verify its
  * own struct declaration at load time. */
 int msa_sizeof(int which);
 

@@ -159,6 +159,7 @@ extern "C" int msa_sizeof(int which) {
     case 0: return static_cast<int>(sizeof(MsaFmhaParams));
     case 1: return static_cast<int>(sizeof(MsaWorkItem));
     case 2: return static_cast<int>(sizeof(MsaPlanArgs));
+    case 3: return static_cast<int>(sizeof(MsaPlanDeviceArgs));
     default: return -1;
   }
 }

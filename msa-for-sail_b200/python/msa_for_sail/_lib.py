@@ -50,10 +50,19 @@ class MsaPlanArgs(ctypes.Structure):
                 ("num_splits", _i32), ("num_sms", _i32), ("reserved", _i32)]
 
 
+class MsaPlanDeviceArgs(ctypes.Structure):
+    _fields_ = [("qo_len", _p), ("kv_len", _p), ("qo_offset_in", _p), ("qo_start", _p), ("kv_start", _p),
+                ("kv_len_out", _p), ("qo_offset_out", _p), ("kv_page_indptr", _p), ("token_batch", _p),
+                ("splits_per_row", _p), ("work", _p), ("batch", _i32), ("num_qo_heads", _i32),
+                ("num_kv_heads", _i32), ("block_m", _i32), ("pack", _i32), ("num_splits", _i32),
+                ("page_size", _i32), ("causal", _i32), ("noncausal_offset", _i32), ("max_total_q", _i32),
+                ("reserved", _i32)]
+
+
 #: every symbol include/msa_b200.h declares
 EXPORTS = ("msa_fmha_fwd", "msa_lse_merge", "msa_topk_select", "msa_plan_dense",
            "msa_status_string", "msa_build_arch", "msa_sizeof", "msa_fmha_fwd_split_static",
-           "msa_sparse_workspace_bytes")
+           "msa_sparse_workspace_bytes", "msa_plan_device")
 
 
 def _load():
@@ -85,6 +94,8 @@ def _load():
     lib.msa_build_arch.restype = ctypes.c_int
     lib.msa_sparse_workspace_bytes.argtypes = [_i64, _i32, _i32, _i32, _i64]
     lib.msa_sparse_workspace_bytes.restype = _i64
+    lib.msa_plan_device.argtypes = [ctypes.POINTER(MsaPlanDeviceArgs), _p]
+    lib.msa_plan_device.restype = ctypes.c_int
     lib.msa_fmha_fwd_split_static.argtypes = [ctypes.POINTER(MsaFmhaParams), _p, _p]
     lib.msa_fmha_fwd_split_static.restype = ctypes.c_int
     return lib

@@ -224,6 +224,20 @@ def _fmha_sail_plan(
                 "graph_safe=True requires qo_offset as a CUDA tensor; an int "
                 "triggers an in-capture allocation")
 
+    if graph_safe:
+        on_dev = (isinstance(qo_segment_lens, torch.Tensor) and qo_segment_lens.is_cuda
+                  and isinstance(kv_segment_lens, torch.Tensor) and kv_segment_lens.is_cuda
+                  and (qo_offset is None or (isinstance(qo_offset, torch.Tensor) and qo_offset.is_cuda)))
+        hkv_ = num_qo_heads if num_kv_heads == -1 else num_kv_heads
+        sparse_ = kv_block_num > 0 and page_size > 0
+        rows_ = max_qo_len_override * _compute_pack_factor(max_qo_len_override, num_qo_heads, hkv_)
+        if on_dev and (sparse_ or rows_ <= 128):
+            return _fmha_sail_plan_device(
+                qo_segment_lens, kv_segment_lens, num_qo_heads, hkv_, qo_offset, num_kv_splits, page_size,
+                output_maxscore, kv_block_num, usable_SM_count, causal, use_fp8_kvcache, dev, given_workspace,
+                max_total_q, max_qo_len_override, bool(qo_len_uniform_override), max_kv_len_override)
+        # longer queries (or host-resident lengths): planned on the host below, which reads the lengths
+
     qo_lens = _to_int_list(qo_segment_lens)
     kv_lens = _to_int_list(kv_segment_lens)
     batch = len(qo_lens)
@@ -401,6 +415,82 @@ def _fmha_sail_plan(
     return info
 
 
+def _fmha_sail_plan_device(qo_segment_lens, kv_segment_lens, num_qo_heads, hkv, qo_offset, num_kv_splits,
+                           page_size, output_maxscore, kv_block_num, usable_SM_count, causal, use_fp8_kvcache,
+                           dev, given_workspace, max_total_q, max_qo, qo_len_uniform, max_kv_len_override):
+    """Graph-safe planner (upstream graph_safe mode, api.py:916-941): the lengths stay on the GPU.
+
+    Everything that sizes a launch comes from the arguments -- batch, ``max_qo_len_override`` (one
+    row tile per batch item), a fixed split count, ``max_total_q`` -- and one kernel
+    (``msa_plan_device``) fills the metadata and the fixed-size work list inside
+    ``given_workspace``.  No host read of device memory and no allocation, so the call can be
+    captured in a CUDA graph together with ``fmha_sail`` and replayed after the length tensors (and
+    the page table) have been updated in place."""
+    batch = int(qo_segment_lens.shape[0])
+    assert kv_segment_lens.shape[0] == batch, "qo_segment_lens and kv_segment_lens must have the same length"
+    for name, t in (("qo_segment_lens", qo_segment_lens), ("kv_segment_lens", kv_segment_lens), ("qo_offset", qo_offset)):
+        if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+            raise ValueError(f"graph_safe=True requires {name} as a contiguous int32 CUDA tensor")
+    h_r = num_qo_heads // hkv
+    is_sparse = kv_block_num > 0 and page_size > 0
+    if is_sparse:
+        pack, block_m = h_r, _block_m(h_r)
+        splits = min(num_kv_splits, kv_block_num) if num_kv_splits >= 1 else 1
+        num_sms = _num_sms(dev)
+        if usable_SM_count > 0:
+            num_sms = min(num_sms, usable_SM_count)
+        while splits > 1 and max_total_q * hkv * (splits // 2) >= num_sms:
+            splits //= 2
+    else:
+        pack = _compute_pack_factor(max_qo, num_qo_heads, hkv)
+        block_m = _block_m(max_qo * pack)
+        splits = num_kv_splits if num_kv_splits >= 1 else 1
+    groups = num_qo_heads // pack
+    arena = _Arena(given_workspace, dev)
+    info = PlanInfo()
+    info["qo_segment_offsets"] = arena.take(batch + 1, torch.int32)
+    info["kv_segment_offsets"] = arena.take(batch + 1, torch.int32)
+    info["qo_segment_lens"] = qo_segment_lens
+    info["kv_segment_lens"] = arena.take(batch, torch.int32)
+    info["qo_offset"] = arena.take(batch, torch.int32)
+    info["kv_page_indptr"] = arena.take(batch + 1, torch.int32) if page_size > 0 else None
+    info["token_batch"] = arena.take(max_total_q, torch.int32) if is_sparse else None
+    splits_per_row = arena.take(max_total_q, torch.int32) if splits > 1 else None
+    n_items = 0 if is_sparse else batch * groups * splits
+    work = arena.take(max(1, n_items) * 8, torch.int32) if not is_sparse else None
+    if splits > 1:
+        info["workspace_o"] = arena.take(splits * max_total_q * num_qo_heads * 128, torch.float32)
+        info["workspace_lse"] = arena.take(splits * max_total_q * num_qo_heads, torch.float32)
+    else:
+        info["workspace_o"] = info["workspace_lse"] = None
+    max_kv = max_kv_len_override
+    a = _lib.MsaPlanDeviceArgs()
+    a.qo_len, a.kv_len, a.qo_offset_in = qo_segment_lens.data_ptr(), kv_segment_lens.data_ptr(), _ptr(qo_offset)
+    a.qo_start, a.kv_start = info["qo_segment_offsets"].data_ptr(), info["kv_segment_offsets"].data_ptr()
+    a.kv_len_out, a.qo_offset_out = info["kv_segment_lens"].data_ptr(), info["qo_offset"].data_ptr()
+    a.kv_page_indptr, a.token_batch = _ptr(info["kv_page_indptr"]), _ptr(info["token_batch"])
+    a.splits_per_row, a.work = _ptr(splits_per_row), _ptr(work)
+    a.batch, a.num_qo_heads, a.num_kv_heads = batch, num_qo_heads, hkv
+    a.block_m, a.pack, a.num_splits = block_m, pack, splits
+    a.page_size, a.causal, a.noncausal_offset = page_size, int(bool(causal)), max(0, max_kv)
+    a.max_total_q = max_total_q
+    _lib.check(_lib.lib.msa_plan_device(ctypes.byref(a), _stream()), "msa_plan_device")
+
+    max_k_tiles = math.ceil(math.ceil(max_kv / KV_TILE) / 128) * 128 if output_maxscore else -1
+    info.update({
+        "qo_tile_size": block_m, "kv_tile_size": KV_TILE, "work": work, "num_work": n_items,
+        "work_tc": None, "num_work_tc": 0, "tc_preferred": False,
+        "page_batch": None, "num_logical_pages": 0, "sparse_tc_preferred": False, "sparse_ws": None,
+        "num_kv_splits": splits, "num_kv_splits_per_row": splits_per_row, "max_qo_len": max_qo,
+        "predicted_speedup": 1.0, "max_k_tiles": max_k_tiles, "pack_factor": pack,
+        "orig_num_qo_heads": num_qo_heads, "num_kv_heads": hkv, "qo_len_uniform": qo_len_uniform,
+        "graph_safe": True, "page_size": page_size, "kv_block_num": kv_block_num if is_sparse else -1,
+        "is_sparse": is_sparse, "total_qo_len": max_total_q, "batch_size": batch, "causal": causal,
+        "_host": None,
+    })
+    return info
+
+
 # ----------------------------------------------------------------------------
 # input validation (upstream _validate_fmha_inputs, api.py:471-768)
 # ----------------------------------------------------------------------------
@@ -564,7 +654,10 @@ def _fmha_sail(
 
     plan = plan_info
     batch = plan["batch_size"]
-    if plan["total_qo_len"] != nnz_qo:
+    if plan["_host"] is None:                 # planned on the device: total_qo_len is the bound max_total_q
+        if nnz_qo > plan["total_qo_len"]:
+            raise ValueError(f"plan allows at most {plan['total_qo_len']} query tokens, q has {nnz_qo}")
+    elif plan["total_qo_len"] != nnz_qo:
         raise ValueError(f"plan was made for {plan['total_qo_len']} query tokens, q has {nnz_qo}")
     if plan["orig_num_qo_heads"] != num_qo_heads or plan["num_kv_heads"] != num_kv_heads:
         raise ValueError("plan head counts do not match q / k")
@@ -585,7 +678,7 @@ def _fmha_sail(
         if qo_offset.dtype != torch.int32:
             qo_offset = qo_offset.to(torch.int32)
 
-    if check_input_valid:
+    if check_input_valid and plan["_host"] is not None:
         _validate_fmha_inputs(q, k, v, plan, is_paged, kv_is_nhd, num_kv_heads, page_size,
                               kv_indices, kv_block_indexes, qo_offset)
 

@@ -33,6 +33,7 @@ def test_struct_sizes_match():
     assert L.lib.msa_sizeof(0) == ctypes.sizeof(L.MsaFmhaParams)
     assert L.lib.msa_sizeof(1) == ctypes.sizeof(L.MsaWorkItem) == 32
     assert L.lib.msa_sizeof(2) == ctypes.sizeof(L.MsaPlanArgs)
+    assert L.lib.msa_sizeof(3) == ctypes.sizeof(L.MsaPlanDeviceArgs)
     assert L.lib.msa_sizeof(99) == -1
 
 
