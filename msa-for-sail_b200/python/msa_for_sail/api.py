@@ -9,6 +9,7 @@ replaced by one prebuilt C-ABI library of sm_100a kernels (see ``_lib``).
 
 import ctypes
 import math
+import os
 from typing import Optional, Tuple, Union
 
 import numpy as np
@@ -48,6 +49,7 @@ def last_status(device=None, reset=True):
     if reset and v:
         w.zero_()
     return v
+_SHOW_PARAMS = os.environ.get("MSA_SHOW_PARAMS", os.environ.get("PPU_LIB_SHOW_PARAMS", "0")) not in ("", "0")
 _PACK_FACTORS = (2, 4, 6, 8, 16)       # upstream jit.py _PACK_FACTORS
 _NUM_SMS = {}
 
@@ -590,6 +592,30 @@ def _scale_arg(x, device, hkv):
     return float(x), None
 
 
+def _show_params(q, plan, is_paged, page_size, sm_scale, output_o, max_score, kv_block_indexes):
+    """Print the call's shape as one '[MSA] --format=...' line (upstream
+    csrc/msa_profiling_interface.hpp:99-157, enabled by PPU_LIB_SHOW_PARAMS=1);
+    ``benchmarks/run_msa.py`` re-runs a call from such a line."""
+    host = plan["_host"]
+    if host is None:
+        return
+    if kv_block_indexes is not None:
+        mode = "Sparse"
+    elif max_score is not None:
+        mode = "Full" if output_o else "OnlyScore"
+    else:
+        mode = "Off"
+    lst = lambda v: "[" + ",".join(str(int(x)) for x in v) + "]"
+    fields = [("dtype", "fp8" if q.dtype == torch.float8_e4m3fn else "bf16"), ("batch_size", plan["batch_size"]),
+              ("seqlen_q", lst(host["qo_lens"])), ("seqlen_k", lst(host["kv_lens"])), ("qo_offset", lst(host["qo_offset"])),
+              ("num_qo_heads", plan["orig_num_qo_heads"]), ("num_kv_heads", plan["num_kv_heads"]),
+              ("head_dim_qk", 128), ("head_dim_vo", 128), ("num_kv_splits", plan["num_kv_splits"]),
+              ("is_paged", int(is_paged)), ("page_size", page_size if is_paged else 0), ("causal", int(plan["causal"])),
+              ("sm_scale", f"{sm_scale:.6f}"), ("sparse_mode", mode),
+              ("kv_block_num", plan["kv_block_num"] if plan["is_sparse"] else 0)]
+    print("[MSA] --format=" + ",".join(f"{k}:{v}" for k, v in fields) + ".", flush=True)
+
+
 def _fmha_sail(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -815,6 +841,8 @@ def _fmha_sail(
     p.sm_scale = float(q_s * k_s * sm_scale)
     p.out_scale = float(v_s * o_s)
 
+    if _SHOW_PARAMS:
+        _show_params(q, plan, is_paged, page_size, float(sm_scale), output_o, max_score, kv_block_indexes)
     stream = _stream()
     _lib.check(_lib.lib.msa_fmha_fwd(ctypes.byref(p), stream), "msa_fmha_fwd")
 

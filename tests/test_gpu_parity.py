@@ -5,6 +5,7 @@ Tolerances: top-k indices bit-exact; bf16 outputs max-abs <= 2e-2 and cosine >= 
 e4m3 operands cosine >= 0.999; max_score within 1e-2 relative.
 """
 import math
+import os
 
 import numpy as np
 import pytest
@@ -540,3 +541,50 @@ def test_msa_pipeline_cpu_reference_config(sparse_path):
                                table.repeat(len(sub)), bi.cpu()[sub], hq,
                                qo_offset=[int(t) for t in sub])
     check_out(out[sub.to(DEV)], ref, "pipeline-o")
+
+
+# ---------------------------------------------------------------------------
+# parameter line -> reproducer
+# ---------------------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["Off", "OnlyScore", "Sparse"])
+def test_param_line_reruns_through_the_reproducer(mode, capsys):
+    """The '[MSA] --format=' line printed for a call is enough to run the same shape again."""
+    import importlib.util
+    from msa_for_sail import api as api_mod
+    api = _api()
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "msa-for-sail_b200", "benchmarks",
+                        "run_msa.py")
+    spec = importlib.util.spec_from_file_location("run_msa", path)
+    run_msa = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(run_msa)
+    g = gen(31)
+    qo_lens, kv_lens, hq, hk, kbn = [1, 3], [700, 1300], 8, 2, 4
+    q = randn_bf16(g, sum(qo_lens), hq, 128)
+    kp, vp, table = make_paged(g, kv_lens, hk, 128)
+    kw = dict(kv_indices=table.to(DEV))
+    plan_kw = dict(num_kv_heads=hk, page_size=128)
+    if mode == "Sparse":
+        offs = [kv_lens[i] - qo_lens[i] for i in range(2)]
+        kw["kv_block_indexes"] = random_blocks(g, qo_lens, kv_lens, offs, hk, kbn).to(DEV)
+        plan_kw["kv_block_num"] = kbn
+    elif mode == "OnlyScore":
+        plan_kw["output_maxscore"] = True
+        kw["output_o"] = False
+    else:
+        kw["output_maxscore"] = False
+    plan = api.fmha_sail_plan(_i32(qo_lens), _i32(kv_lens), hq, **plan_kw)
+    old = api_mod._SHOW_PARAMS
+    api_mod._SHOW_PARAMS = True
+    try:
+        api.fmha_sail(q.to(DEV), kp.to(DEV), vp.to(DEV), plan, **kw)
+    finally:
+        api_mod._SHOW_PARAMS = old
+    lines = [ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("[MSA] --format=")]
+    assert len(lines) == 1
+    cfg = run_msa.parse_format(lines[0])
+    assert cfg["seqlen_q"] == qo_lens and cfg["seqlen_k"] == kv_lens and cfg["sparse_mode"] == mode
+    assert cfg["num_qo_heads"] == hq and cfg["num_kv_heads"] == hk
+    run_msa.build_and_run(cfg)
+    assert "RAN OK" in capsys.readouterr().out
