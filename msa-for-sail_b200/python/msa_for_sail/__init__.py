@@ -15,3 +15,7 @@ from .api import (  # noqa: F401
 
 __all__ = ["fmha_sail_plan", "fmha_sail", "sparse_topk_select", "allocate_graph_workspace"]
 __version__ = "0.1.0"
+
+# TVM-FFI global functions minfer.ops.* (upstream __init__.py:20-78); a no-op without tvm_ffi
+from . import ffi as _ffi  # noqa: E402
+_ffi.register()
