@@ -2,7 +2,7 @@
 """Generate the golden fixtures in this directory from the UPSTREAM reference.
 
 Run once, in a container that has the upstream tree checked out (path given by
-``--reference``, default ``/root/reference``); the resulting ``*.npz`` files are
+``--reference`` or the environment variable ``MSA_REFERENCE_DIR``); the resulting ``*.npz`` files are
 committed so that the test-suite never needs the upstream tree.
 
 Every expected value here is produced by the upstream project's own PyTorch
@@ -35,7 +35,8 @@ def bf16_bits(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MSA_REFERENCE_DIR"), required="MSA_REFERENCE_DIR" not in os.environ,
+                    help="directory of the upstream checkout")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "tests"))
     sys.path.insert(0, os.path.join(args.reference, "tests", "regression"))
