@@ -170,17 +170,20 @@ int msa_plan_dense(const MsaPlanArgs* args, MsaWorkItem* work, int32_t capacity,
 /* Planning on the device, for callers that capture plan + run into one CUDA graph and only
  * update the length tensors between replays (upstream: `graph_safe=True`, the
  * prepare_plan_metadata + plan kernels, api.py:916-941, 1040-1048, 1196-1203).
- * Everything that sizes a launch is fixed when the graph is built: batch, the row tile
- * (one tile of block_m rows per batch item: qo_len * pack <= block_m), the split count.
+ * Everything that sizes a launch is fixed when the graph is built: batch, the number of
+ * row tiles per batch item (`row_tiles` >= ceil(max qo_len * pack / block_m)), the split count.
  * One kernel launch on `stream`; reads no device memory on the host, allocates nothing.
  * Fills, for i in [0, batch):  qo_start / kv_start (exclusive prefix sums, [batch + 1]),
  * kv_len_out, qo_offset_out (causal: kv_len - qo_len where qo_offset_in is NULL or
  * negative; non-causal: `noncausal_offset`), kv_page_indptr ([batch + 1], pages of
  * `page_size` keys, NULL for ragged K/V), token_batch ([max_total_q], NULL when unused),
  * splits_per_row ([max_total_q], = num_splits) and the work list: exactly
- * batch * (num_qo_heads / pack) * num_splits items, item ((b * groups) + g) * S + s
- * covering the s-th of S equal chunks of the key tiles batch item b can see (empty range
- * when it has fewer tiles).  NULL outputs are skipped. */
+ * batch * row_tiles * (num_qo_heads / pack) * num_splits items, item
+ * (((b * row_tiles + r) * groups) + g) * S + s = row tile (row_tiles - 1 - r) of batch item b
+ * (later rows first: under a causal mask they see more keys), head group g, the s-th of S
+ * equal chunks of the key tiles those rows can see.  A row tile past the item's rows, or a
+ * chunk past its tiles, is an item with num_rows = 0 / an empty tile range.  NULL outputs
+ * are skipped. */
 typedef struct MsaPlanDeviceArgs {
   const int32_t* qo_len;       /* [B] device */
   const int32_t* kv_len;       /* [B] device */
@@ -200,7 +203,7 @@ typedef struct MsaPlanDeviceArgs {
   int32_t causal;
   int32_t noncausal_offset;
   int32_t max_total_q;
-  int32_t reserved;
+  int32_t row_tiles;           /* >= 1 */
 } MsaPlanDeviceArgs;
 int msa_plan_device(const MsaPlanDeviceArgs* args, msa_stream_t stream);
 

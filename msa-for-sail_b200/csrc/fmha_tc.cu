@@ -130,7 +130,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     // =========================== TMA producer ===========================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (lane == 0) { tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); }
-    if (elect_one()) {
+    if (n_total > 0 && elect_one()) {                   // an item without visible keys loads nothing
       mbar_arrive_expect_tx(bar(Q_FULL), 2 * TILE_BYTES);
 #pragma unroll
       for (int x = 0; x < 2; ++x)

@@ -56,7 +56,7 @@ class MsaPlanDeviceArgs(ctypes.Structure):
                 ("splits_per_row", _p), ("work", _p), ("batch", _i32), ("num_qo_heads", _i32),
                 ("num_kv_heads", _i32), ("block_m", _i32), ("pack", _i32), ("num_splits", _i32),
                 ("page_size", _i32), ("causal", _i32), ("noncausal_offset", _i32), ("max_total_q", _i32),
-                ("reserved", _i32)]
+                ("row_tiles", _i32)]
 
 
 #: every symbol include/msa_b200.h declares

@@ -146,7 +146,7 @@ class _Arena:
 
 def _workspace_bytes(batch, total_q, num_qo_heads, splits, sparse):
     meta = (5 * (batch + 1) + 2 * total_q) * 4 + 256 * 8
-    work = 0 if sparse else max(1, total_q) * num_qo_heads * max(1, splits) * 32
+    work = 0 if sparse else 2 * max(1, total_q) * num_qo_heads * max(1, splits) * 32   # both work lists
     part = 0 if splits <= 1 else splits * total_q * num_qo_heads * (128 + 1) * 4
     return meta + work + part + 4096
 
@@ -231,14 +231,12 @@ def _fmha_sail_plan(
                   and isinstance(kv_segment_lens, torch.Tensor) and kv_segment_lens.is_cuda
                   and (qo_offset is None or (isinstance(qo_offset, torch.Tensor) and qo_offset.is_cuda)))
         hkv_ = num_qo_heads if num_kv_heads == -1 else num_kv_heads
-        sparse_ = kv_block_num > 0 and page_size > 0
-        rows_ = max_qo_len_override * _compute_pack_factor(max_qo_len_override, num_qo_heads, hkv_)
-        if on_dev and (sparse_ or rows_ <= 128):
+        if on_dev:
             return _fmha_sail_plan_device(
                 qo_segment_lens, kv_segment_lens, num_qo_heads, hkv_, qo_offset, num_kv_splits, page_size,
                 output_maxscore, kv_block_num, usable_SM_count, causal, use_fp8_kvcache, dev, given_workspace,
                 max_total_q, max_qo_len_override, bool(qo_len_uniform_override), max_kv_len_override)
-        # longer queries (or host-resident lengths): planned on the host below, which reads the lengths
+        # host-resident lengths: planned on the host below, which reads them
 
     qo_lens = _to_int_list(qo_segment_lens)
     kv_lens = _to_int_list(kv_segment_lens)
@@ -422,8 +420,8 @@ def _fmha_sail_plan_device(qo_segment_lens, kv_segment_lens, num_qo_heads, hkv, 
                            dev, given_workspace, max_total_q, max_qo, qo_len_uniform, max_kv_len_override):
     """Graph-safe planner (upstream graph_safe mode, api.py:916-941): the lengths stay on the GPU.
 
-    Everything that sizes a launch comes from the arguments -- batch, ``max_qo_len_override`` (one
-    row tile per batch item), a fixed split count, ``max_total_q`` -- and one kernel
+    Everything that sizes a launch comes from the arguments -- batch, ``max_qo_len_override`` (the
+    row tiles per batch item), a fixed split count, ``max_total_q`` -- and one kernel
     (``msa_plan_device``) fills the metadata and the fixed-size work list inside
     ``given_workspace``.  No host read of device memory and no allocation, so the call can be
     captured in a CUDA graph together with ``fmha_sail`` and replayed after the length tensors (and
@@ -448,6 +446,12 @@ def _fmha_sail_plan_device(qo_segment_lens, kv_segment_lens, num_qo_heads, hkv, 
         block_m = _block_m(max_qo * pack)
         splits = num_kv_splits if num_kv_splits >= 1 else 1
     groups = num_qo_heads // pack
+    bm_eff = (block_m // pack) * pack
+    row_tiles = max(1, -(-(max_qo * pack) // bm_eff))
+    # long bf16 queries on 128-key pages (or ragged K/V): also a list of 256-row items for the tcgen05
+    # prefill kernel, one query head per row tile, unsplit
+    want_tc = (not is_sparse and pack == 1 and max_qo > 128 and not use_fp8_kvcache and page_size in (-1, 0, 128)
+               and splits == 1)
     arena = _Arena(given_workspace, dev)
     info = PlanInfo()
     info["qo_segment_offsets"] = arena.take(batch + 1, torch.int32)
@@ -458,8 +462,11 @@ def _fmha_sail_plan_device(qo_segment_lens, kv_segment_lens, num_qo_heads, hkv, 
     info["kv_page_indptr"] = arena.take(batch + 1, torch.int32) if page_size > 0 else None
     info["token_batch"] = arena.take(max_total_q, torch.int32) if is_sparse else None
     splits_per_row = arena.take(max_total_q, torch.int32) if splits > 1 else None
-    n_items = 0 if is_sparse else batch * groups * splits
+    n_items = 0 if is_sparse else batch * row_tiles * groups * splits
     work = arena.take(max(1, n_items) * 8, torch.int32) if not is_sparse else None
+    tc_tiles = max(1, -(-max_qo // 256))
+    n_items_tc = batch * tc_tiles * num_qo_heads if want_tc else 0
+    work_tc = arena.take(n_items_tc * 8, torch.int32) if want_tc else None
     if splits > 1:
         info["workspace_o"] = arena.take(splits * max_total_q * num_qo_heads * 128, torch.float32)
         info["workspace_lse"] = arena.take(splits * max_total_q * num_qo_heads, torch.float32)
@@ -475,13 +482,21 @@ def _fmha_sail_plan_device(qo_segment_lens, kv_segment_lens, num_qo_heads, hkv, 
     a.batch, a.num_qo_heads, a.num_kv_heads = batch, num_qo_heads, hkv
     a.block_m, a.pack, a.num_splits = block_m, pack, splits
     a.page_size, a.causal, a.noncausal_offset = page_size, int(bool(causal)), max(0, max_kv)
-    a.max_total_q = max_total_q
+    a.max_total_q, a.row_tiles = max_total_q, row_tiles
     _lib.check(_lib.lib.msa_plan_device(ctypes.byref(a), _stream()), "msa_plan_device")
+    if want_tc:
+        t = _lib.MsaPlanDeviceArgs()
+        t.qo_len, t.kv_len, t.qo_offset_in = a.qo_len, a.kv_len, a.qo_offset_in
+        t.work = work_tc.data_ptr()
+        t.batch, t.num_qo_heads, t.num_kv_heads = batch, num_qo_heads, hkv
+        t.block_m, t.pack, t.num_splits, t.row_tiles = 256, 1, 1, tc_tiles
+        t.page_size, t.causal, t.noncausal_offset, t.max_total_q = page_size, a.causal, a.noncausal_offset, 0
+        _lib.check(_lib.lib.msa_plan_device(ctypes.byref(t), _stream()), "msa_plan_device")
 
     max_k_tiles = math.ceil(math.ceil(max_kv / KV_TILE) / 128) * 128 if output_maxscore else -1
     info.update({
         "qo_tile_size": block_m, "kv_tile_size": KV_TILE, "work": work, "num_work": n_items,
-        "work_tc": None, "num_work_tc": 0, "tc_preferred": False,
+        "work_tc": work_tc, "num_work_tc": n_items_tc, "tc_preferred": want_tc,
         "page_batch": None, "num_logical_pages": 0, "sparse_tc_preferred": False, "sparse_ws": None,
         "num_kv_splits": splits, "num_kv_splits_per_row": splits_per_row, "max_qo_len": max_qo,
         "predicted_speedup": 1.0, "max_k_tiles": max_k_tiles, "pack_factor": pack,
