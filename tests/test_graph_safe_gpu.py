@@ -156,7 +156,7 @@ def test_plan_device_fills_what_its_header_says(causal, paged):
     a.kv_page_indptr = indptr.data_ptr() if paged else None
     a.token_batch, a.splits_per_row, a.work = token_batch.data_ptr(), spr.data_ptr(), work.data_ptr()
     a.batch, a.num_qo_heads, a.num_kv_heads, a.block_m, a.pack, a.num_splits = batch, hq, hk, block_m, pack, S
-    a.page_size, a.causal, a.noncausal_offset, a.max_total_q = page, int(causal), 4000, max_total_q
+    a.page_size, a.causal, a.noncausal_offset, a.max_total_q, a.row_tiles = page, int(causal), 4000, max_total_q, 1
     assert _lib.lib.msa_plan_device(ctypes.byref(a), torch.cuda.current_stream().cuda_stream) == 0
     torch.cuda.synchronize()
     exp_off = np.where(off_in < 0, kl - ql, off_in) if causal else np.full(batch, 4000)
