@@ -377,6 +377,7 @@ def test_sparse_golden(sparse_path):
     ([1, 1, 1], [3000, 129, 5000], 64, 8, 16, 4, True),      # e4m3 decode, 8 rows per item, -1 padded lists
     ([1, 1, 1], [3000, 129, 5000], 64, 8, 16, 4, False),     # same on a bf16 cache
     ([2, 1], [1000, 4100], 32, 2, 8, 1, True),               # e4m3, 16 rows per item, two tokens
+    ([40, 3], [6000, 4500], 8, 2, 32, 1, False),             # 32 selected pages per token
 ])
 def test_sparse_matches_oracle(qo_lens, kv_lens, hq, hk, kbn, splits, fp8, sparse_path):
     api = _api()
