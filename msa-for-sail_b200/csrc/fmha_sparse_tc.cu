@@ -9,17 +9,17 @@
 // memory while it streams chunks of 128/G query tokens (G = Hq/Hkv rows each) that selected it:
 //
 //   S = Q_chunk K_page^T  (tcgen05, TMEM)  ->  mask on original positions, softmax of the one
-//   tile  ->  O = P V_page  ->  normalised partial O (bf16) + LSE, stored in the order of the
-//   sorted selection list (a chunk's 128 rows are one contiguous 32 KB block: two TMA stores)
+//   tile  ->  O = P V_page  ->  normalised partial O (bf16) + LSE, stored token-major at
+//   [token][kv head][slot][head in group] (one TMA box per 8 rows: the heads of a token)
 //
-// and a merge kernel combines the `kv_block_num` partials of every row through the inverse map
-// (token, kv head, slot) -> position in the sorted list.  Every (token, page) pair is computed
-// exactly once regardless of how the selections overlap.
+// and a merge kernel streams that buffer once: the `kv_block_num` partials of a (token, kv head)
+// are one contiguous block, a bit mask per (token, kv head) says which slots were computed.
+// Every (token, page) pair is computed exactly once regardless of how the selections overlap.
 //
 // Kernels in this file: count / scan / scatter (counting sort of the selections by page), the merge and the
 // attention kernel.  Roles of the attention kernel (20 warps): warps 0-3 / 4-7 softmax of even / odd
 // chunks (152 registers each: a whole row of S is held at once); warps 8-11 / 12-15 epilogue of
-// head_dim [0, 64) / [64, 128) (O out of TMEM, bf16, shared memory, one TMA tensor store per chunk
+// head_dim [0, 64) / [64, 128) (O out of TMEM, bf16, shared memory, one TMA tensor store per token
 // and half, overlapping the softmax of later chunks); warps 16-18 loaders (the page by TMA, once;
 // the Q rows of a chunk gathered with one TMA box per 8 rows, the boxes spread over the lanes of
 // three warps because a warp issues its lanes' boxes one after another); warp 19 MMA issuer.
@@ -38,36 +38,45 @@ using namespace tc;
 constexpr int BM = 128, BN = 128;
 constexpr int SUB_BYTES = BM * 64 * 2;
 constexpr int TILE_BYTES = 2 * SUB_BYTES;
-constexpr int OFF_Q = 0;                        // two Q chunk buffers
-constexpr int OFF_K = 2 * TILE_BYTES;
-constexpr int OFF_V = 3 * TILE_BYTES;
-constexpr int OFF_STAGE = 4 * TILE_BYTES;       // two buffers of 128 rows x 256 B of bf16 O on their way out
-// what the softmax warpgroups hand to the epilogue warpgroup, per row, for the 4 chunks in flight
-struct RowMeta { float inv; float lse; };
-constexpr int OFF_META = OFF_STAGE + 2 * TILE_BYTES;    // [4][128] RowMeta
-constexpr int OFF_BAR = OFF_META + 4 * BM * 8;
+constexpr int NWG = 3;                          // softmax + epilogue warpgroups; warpgroup x owns chunks c % 3 == x
+constexpr int NSBUF = NWG;                      // S / P buffers in TMEM, one per warpgroup
+constexpr int NQBUF = 2;                        // Q chunk buffers
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = NQBUF * TILE_BYTES;
+constexpr int OFF_V = OFF_K + TILE_BYTES;
+// bf16 O on its way out: [128 rows][256 B] per warpgroup, the 16-byte pieces of a row XOR-ed with
+// (head & 7).  (Two buffers shared by the three warpgroups would leave room for a third Q buffer, but
+// a warpgroup then waits for another one's bulk copies to be read, ~1 000 clocks: slower.)
+constexpr int OFF_STAGE = OFF_V + TILE_BYTES;
+constexpr int OFF_BAR = OFF_STAGE + NWG * TILE_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-constexpr int NTHREADS = 640;
-constexpr int EPI_WARP0 = 8, GATHER_WARP0 = 16, GATHER_WARPS = 3, MMA_WARP = 19;
+// 512 threads start with 128 registers each (65 536 in all); setmaxnreg then moves them between the
+// roles.  The sum after the moves must stay within what the launch allocated, or the increase
+// never completes: the launcher checks the compiled register count before it launches.
+constexpr int NTHREADS = 512;
+constexpr int GATHER_WARP0 = 4 * NWG, GATHER_WARPS = 3, MMA_WARP = GATHER_WARP0 + GATHER_WARPS;
 constexpr int GATHER_THREADS = GATHER_WARPS * 32;
+constexpr int REGS_SOFTMAX = 152, REGS_OTHER = 40;
+constexpr int REGS_NEEDED = NWG * 128 * REGS_SOFTMAX + (GATHER_WARPS + 1) * 32 * REGS_OTHER;
+static_assert(NTHREADS == (MMA_WARP + 1) * 32, "warp roles");
+static_assert(REGS_NEEDED <= 65536, "setmaxnreg budget");
 constexpr int ITEM_CHUNKS = 32;                 // chunks of 128 rows per work item
 constexpr uint32_t kEmuMask = 0x5252;
 
-// TMEM: three S buffers (chunk c uses c % 3; P_c overwrites the front of S_c) and one O, drained by
-// two warpgroups (64 columns each).  With only two S buffers Q_{c+2} K^T would have to wait for P_c V, which puts the softmax of a
-// warpgroup, that MMA and the next Q K^T on one serial chain.
-constexpr int NSBUF = 3;
+// TMEM: three S buffers (P_c overwrites the front of S_c) and one O.  Q_{c+3} K^T reuses the buffer of
+// chunk c, so it follows P_c V directly in the MMA warp's program and is ready long before its
+// warpgroup asks.
 constexpr uint32_t O_COL = NSBUF * BN;
-// META_FULL has one barrier per chunk in flight (c & 3): the softmax warpgroups run ahead of the
-// epilogue, and a barrier that completed twice since the waiter last looked reads as "not yet".
+// O_FULL has one barrier per warpgroup: a warpgroup that finished P_c may come to wait for O_c while
+// O_{c-2} is the latest completion, and a single barrier would read as "done" (same parity).
 enum Bar { K_FULL = 0, V_FULL = 1, V_FIX = 2, Q_FULL = 3, Q_EMPTY = 5, S_FULL = 7, P_FULL = 10, O_FULL = 13,
-           O_FREE = 14, META_FULL = 15, NUM_BARS = 19 };
+           O_FREE = 16, NUM_BARS = 17 };
 
 // test hook: take the global-atomics index kernels even when the histogram fits shared memory
 bool g_force_global_index = false;
 
-// optional clock trace of one CTA (debugging aid): [6 roles][512 chunks][8 tags]; roles: softmax 0/1,
-// MMA 2, loaders 3, epilogue 4
+// optional clock trace of one CTA (debugging aid): [6 roles][512 chunks][8 tags]; roles: warpgroups 0-2,
+// MMA 3, loaders 4
 __device__ unsigned long long g_trace[6 * 512 * 8];
 __device__ int g_trace_cta = -1;
 
@@ -78,9 +87,9 @@ struct Ws {                 // device workspace carved by carve()
   int32_t* part_start;      // [Hkv + 1]  first work item of every kv head, then the item count
   int4* items;              // [max_items] {bin, entry_begin, entry_end, 0}
   int32_t* entries;         // [cap]  token << 5 | slot, sorted by (kv head, page); gaps between bins are padding
-  int32_t* inv;             // [T, Hkv, kbn]  position of a selection in `entries`, -1 if it selects nothing
-  float* partial_lse;       // [cap * G]   row = position * G + head in group
-  __nv_bfloat16* partial_o; // [cap * G, 128]
+  int32_t* vmask;           // [T, Hkv]  bit s: slot s of this (token, kv head) selects a visible page
+  float* partial_lse;       // [T, Hkv, kbn, G]
+  __nv_bfloat16* partial_o; // [T, Hkv, kbn, G, 128]
   int64_t cap;              // entries incl. padding
   int64_t max_items;
   int64_t total_bytes;
@@ -105,9 +114,9 @@ Ws carve(void* base, int64_t T, int Hq, int Hkv, int kbn, int64_t NP) {
   w.bin_cursor = reinterpret_cast<int32_t*>(take(NB * 4));
   w.items = reinterpret_cast<int4*>(take(w.max_items * 16));
   w.entries = reinterpret_cast<int32_t*>(take(w.cap * 4));
-  w.inv = reinterpret_cast<int32_t*>(take(T * Hkv * kbn * 4));
-  w.partial_lse = reinterpret_cast<float*>(take(w.cap * G * 4));
-  w.partial_o = reinterpret_cast<__nv_bfloat16*>(take(w.cap * G * kHeadDim * 2));
+  w.vmask = reinterpret_cast<int32_t*>(take(T * Hkv * 4));
+  w.partial_lse = reinterpret_cast<float*>(take(T * Hkv * kbn * G * 4));
+  w.partial_o = reinterpret_cast<__nv_bfloat16*>(take(T * Hkv * kbn * G * kHeadDim * 2));
   w.total_bytes = off;
   return w;
 }
@@ -133,7 +142,7 @@ __device__ __forceinline__ bool entry_valid(const IndexArgs& a, int t, int b, in
 template <bool SCATTER>
 __global__ void __launch_bounds__(256)
 sparse_index_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t* __restrict__ bin_cursor,
-                    int32_t* __restrict__ entries, int32_t* __restrict__ inv) {
+                    int32_t* __restrict__ entries, int32_t* __restrict__ vmask) {
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // kvh-major, token fastest
   const int64_t n = static_cast<int64_t>(a.total_q) * a.num_kv_heads;
   if (gid >= n) return;
@@ -141,22 +150,17 @@ sparse_index_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t*
   const int b = a.token_batch[t];
   const int page_base = a.kv_page_indptr[b];
   const int32_t* row = a.kbi + static_cast<int64_t>(t) * a.kbi_stride_tok + static_cast<int64_t>(kvh) * a.kbi_stride_head;
-  int32_t* inv_row = inv + (static_cast<int64_t>(t) * a.num_kv_heads + kvh) * a.kbn;
+  uint32_t mask = 0;
   for (int s = 0; s < a.kbn; ++s) {
     const int blk = row[s];
     if (entry_valid(a, t, b, blk)) {
       const int bin = kvh * a.num_pages + page_base + blk;
-      if (SCATTER) {
-        const int pos = atomicAdd(&bin_cursor[bin], 1);
-        entries[pos] = (t << 5) | s;
-        inv_row[s] = pos;
-      } else {
-        atomicAdd(&bin_count[bin], 1);
-      }
-    } else if (SCATTER) {
-      inv_row[s] = -1;                                       // this slot contributes nothing to the merge
+      mask |= 1u << s;
+      if (SCATTER) entries[atomicAdd(&bin_cursor[bin], 1)] = (t << 5) | s;
+      else atomicAdd(&bin_count[bin], 1);
     }
   }
+  if (SCATTER) vmask[static_cast<int64_t>(t) * a.num_kv_heads + kvh] = static_cast<int32_t>(mask);
 }
 
 // The same two passes with a shared-memory histogram: a CTA owns 256 consecutive tokens of one kv
@@ -166,7 +170,7 @@ sparse_index_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t*
 template <bool SCATTER, int KBN>
 __global__ void __launch_bounds__(256)
 sparse_index_smem_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t* __restrict__ bin_cursor,
-                         int32_t* __restrict__ entries, int32_t* __restrict__ inv) {
+                         int32_t* __restrict__ entries, int32_t* __restrict__ vmask) {
   extern __shared__ int32_t s_hist[];                      // [num_pages] count, then (scatter) next position
   const int blocks_per_head = (a.total_q + 255) / 256;
   const int kvh = blockIdx.x / blocks_per_head;
@@ -199,18 +203,15 @@ sparse_index_smem_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int
   if (!SCATTER) return;
   __syncthreads();
   if (t < a.total_q) {
-    int32_t* inv_row = inv + (static_cast<int64_t>(t) * a.num_kv_heads + kvh) * a.kbn;
+    uint32_t mask = 0;
 #pragma unroll
     for (int s = 0; s < KBN; ++s) {
-      if (s < a.kbn) {
-        int pos = -1;
-        if (gpage[s] >= 0) {
-          pos = atomicAdd(&s_hist[gpage[s]], 1);
-          entries[pos] = (t << 5) | s;
-        }
-        inv_row[s] = pos;
+      if (s < a.kbn && gpage[s] >= 0) {
+        entries[atomicAdd(&s_hist[gpage[s]], 1)] = (t << 5) | s;
+        mask |= 1u << s;
       }
     }
+    vmask[static_cast<int64_t>(t) * a.num_kv_heads + kvh] = static_cast<int32_t>(mask);
   }
 }
 
@@ -256,39 +257,38 @@ sparse_scan_kernel(const int32_t* __restrict__ bin_count, int32_t* __restrict__ 
 
 // ------------------------------------------------------------------------------------------
 // merge: out[t, h] = sum_s w_s O_s / sum_s w_s over the selections of (t, kv head), w_s = exp(lse_s - max)
-// Half a warp per (token, head) row, lane l of the half owns columns 8l..8l+7; the partial rows are
-// found through `inv`.  All loads of a row are issued before any is used.
+// Half a warp per (token, head) row, lane l of the half owns columns 8l..8l+7.  Rows are walked in
+// output order, which is also the order of the partial buffer: the kbn x G partial rows of a
+// (token, kv head) are one contiguous block, so the pass streams.  All loads of a row are issued
+// before any is used.
 // ------------------------------------------------------------------------------------------
 template <int KBN>
 __global__ void __launch_bounds__(256)
-sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restrict__ pl, const int32_t* __restrict__ inv,
+sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restrict__ pl, const int32_t* __restrict__ vmask,
                     __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int kbn, int total_q, int num_heads,
-                    int num_kv_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale, int kvh0, int nkvh) {
+                    int num_kv_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale) {
   const int l16 = threadIdx.x & 15;
-  // rows are walked kv-head-major: the partials of one kv head are one contiguous eighth (1 / Hkv) of
-  // the buffer, which keeps the randomly gathered 2 KB reads of a pass within reach of the TLB.
-  // This launch covers kv heads [kvh0, kvh0 + nkvh); a small grid strides over them (used while the
-  // attention kernel of the next kv head runs on the other SMs).
   const int G = num_heads / num_kv_heads;
-  const int64_t n_idx = static_cast<int64_t>(total_q) * G * nkvh;
+  const int64_t n_idx = static_cast<int64_t>(total_q) * num_heads;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4); idx < n_idx;
        idx += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 4)) {
-  const int g = static_cast<int>(idx % G);
-  const int64_t tg = idx / G;
-  const int kvh = kvh0 + static_cast<int>(tg / total_q), t = static_cast<int>(tg % total_q);
-  const int h = kvh * G + g;
-  const int64_t row = static_cast<int64_t>(t) * num_heads + h;
-  const int32_t* iv = inv + (static_cast<int64_t>(t) * num_kv_heads + kvh) * kbn;
+  const int t = static_cast<int>(idx / num_heads), h = static_cast<int>(idx % num_heads);
+  const int kvh = h / G, g = h % G;
+  const int64_t row = idx;
+  const int64_t tk = static_cast<int64_t>(t) * num_kv_heads + kvh;
+  const uint32_t mask = static_cast<uint32_t>(__ldg(vmask + tk));
+  const int64_t prow0 = tk * kbn * G + g;                   // slot s of this row: prow0 + s * G
+  const int piece = l16 ^ (g & 7);                          // the attention kernel stores a row's 16-byte pieces XOR-ed with (head & 7)
   float lse[KBN];
   uint4 raw[KBN];
   float mx = -INFINITY;
 #pragma unroll
   for (int s = 0; s < KBN; ++s) {
-    const int pos = s < kbn ? iv[s] : -1;
-    const int64_t prow = static_cast<int64_t>(max(pos, 0)) * G + g;             // clamped: always a readable row
-    raw[s] = *reinterpret_cast<const uint4*>(po + prow * kHeadDim + l16 * 8);
+    const bool have = s < kbn && ((mask >> s) & 1u);
+    const int64_t prow = prow0 + static_cast<int64_t>(s < kbn ? s : 0) * G;   // always a readable row; unused if !have
+    raw[s] = *reinterpret_cast<const uint4*>(po + prow * kHeadDim + piece * 8);
     const float l = __ldg(pl + prow);
-    lse[s] = pos >= 0 ? l : -INFINITY;
+    lse[s] = have ? l : -INFINITY;
     mx = fmaxf(mx, lse[s]);
   }
   const float mxs = (mx == -INFINITY) ? 0.f : mx;
@@ -327,9 +327,9 @@ sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restric
 __global__ void __launch_bounds__(NTHREADS, 1)
 sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                 const __grid_constant__ CUtensorMap tm_o, const int4* __restrict__ items, const int32_t* __restrict__ part_start,
-                 const int part,
-                 const int32_t* __restrict__ entries, float* __restrict__ partial_lse) {
+                 const int4* __restrict__ items, const int32_t* __restrict__ part_start, const int part,
+                 const int32_t* __restrict__ entries, float* __restrict__ partial_lse,
+                 __nv_bfloat16* __restrict__ partial_o) {
   // this launch covers the work items of kv head `part`, or all of them (part < 0)
   const int item_idx = (part >= 0 ? part_start[part] : 0) + static_cast<int>(blockIdx.x);
   if (item_idx >= part_start[part >= 0 ? part + 1 : p.num_kv_heads]) return;   // uniform: before any barrier / TMEM use
@@ -370,10 +370,11 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     *skip_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
   if (threadIdx.x == 0) {
     mbar_init(bar(K_FULL), 1); mbar_init(bar(V_FULL), 1); mbar_init(bar(V_FIX), 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(bar(Q_FULL + s), 1);  mbar_init(bar(Q_EMPTY + s), 1); }
-    for (int s = 0; s < NSBUF; ++s) { mbar_init(bar(S_FULL + s), 1);  mbar_init(bar(P_FULL + s), BM); }
-    for (int s = 0; s < 4; ++s) mbar_init(bar(META_FULL + s), BM);
-    mbar_init(bar(O_FULL), 1);  mbar_init(bar(O_FREE), 2 * BM);       // both epilogue warpgroups drain O
+    for (int s = 0; s < NQBUF; ++s) { mbar_init(bar(Q_FULL + s), 1);  mbar_init(bar(Q_EMPTY + s), 1); }
+    for (int s = 0; s < NSBUF; ++s) {
+      mbar_init(bar(S_FULL + s), 1);  mbar_init(bar(P_FULL + s), BM);  mbar_init(bar(O_FULL + s), 1);
+    }
+    mbar_init(bar(O_FREE), BM);                                      // the warpgroup of the chunk drains O
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -437,16 +438,18 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       const int e = item.y + c * tpc + unit / upt;
       return (c < n_chunks && unit8 && unit < BM / 8 && e < item.z) ? entries[e] : -1;
     };
+    // (Prefetching the boxes of the next chunk into L2 was tried: the loaders' time goes into issuing
+    // boxes, ~150 clocks each within a warp, and twice as many made the gather later, not earlier.)
     int ent = entry_of(0);
     for (int c = 0; c < n_chunks && alive; ++c) {
-      const int x = c & 1, u = c >> 1;
-      if (gt == 0) trace(3, c, 0);
-      alive = mbar_wait(bar(Q_EMPTY + x), (u & 1) ^ 1, abort_flag);   // Q K^T of chunk c - 2 has read the buffer
+      const int x = c % NQBUF, u = c / NQBUF;
+      if (gt == 0) trace(4, c, 0);
+      alive = mbar_wait(bar(Q_EMPTY + x), (u & 1) ^ 1, abort_flag);   // Q K^T of chunk c - 3 has read the buffer
       if (!alive) break;
       const int e0 = item.y + c * tpc;
       const int ntok = min(tpc, item.z - e0);
       if (gt == 0) {
-        trace(3, c, 1);
+        trace(4, c, 1);
         mbar_arrive_expect_tx(bar(Q_FULL + x), ntok * G * 256);
       }
       if (unit8) {
@@ -490,130 +493,99 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       for (int k = 0; k < 8; ++k)
         mma_ts(tmem + O_COL, tmem + sb * BN + k * 8, dv_hi | ((va + k * (2048 >> 4)) & 0x3FFF), IDESC_PV, k > 0 ? 1u : 0u);
     };
+    // Two streams share this warp: S_c = Q_c K^T (c may run three chunks ahead of the other stream:
+    // S_{c+3} reuses the buffer of P_c, so it must follow P_c V in issue order) and O_d = P_d V (needs P_d
+    // from its warpgroup and O of chunk d - 1 drained).  Each has waits of its own -- the Q gather on
+    // one side, the drain of O on the other -- so the warp polls both and issues whichever is ready
+    // instead of blocking on one in a fixed order.
     bool alive = mbar_wait(bar(K_FULL), 0, abort_flag);
-    // S[c % 3] = Q_c K^T.  Issued three chunks ahead of the P V stream: S_{c+3} reuses the buffer
-    // of chunk c, so it may follow P_c V directly and is ready long before its warpgroup asks.
-    auto do_qk = [&](int c) {
-      const int x = c & 1, u = c >> 1;
-      if (lane == 0) trace(2, c, 0);
-      alive = mbar_wait(bar(Q_FULL + x), u & 1, abort_flag);
-      if (lane == 0) trace(2, c, 2);
-      if (!alive) return;
-      tc_fence_after();
-      if (elect_one()) {
-        issue_qk(x, c % NSBUF);
-        mma_commit(bar(S_FULL + c % NSBUF));
-        mma_commit(bar(Q_EMPTY + x));
-      }
-      __syncwarp();
-    };
-    for (int c = 0; c < NSBUF && c < n_chunks && alive; ++c) do_qk(c);
-    for (int d = 0; d < n_chunks && alive; ++d) {           // O = P_d V, once the epilogue has drained O of chunk d - 1
-      if (d == 0) alive = mbar_wait(bar(V_FULL), 0, abort_flag);
-      if (lane == 0) trace(2, d, 3);
-      if (alive) alive = mbar_wait(bar(P_FULL + d % NSBUF), (d / NSBUF) & 1, abort_flag);
-      if (lane == 0) trace(2, d, 4);
-      if (alive && d > 0) alive = mbar_wait(bar(O_FREE), (d - 1) & 1, abort_flag);
-      if (!alive) break;
-      tc_fence_after();
-      if (elect_one()) {
-        issue_pv(d % NSBUF);
-        mma_commit(bar(O_FULL));
-      }
-      __syncwarp();
-      if (lane == 0) trace(2, d, 5);
-      if (d + NSBUF < n_chunks) do_qk(d + NSBUF);
-    }
-  } else if (warp >= EPI_WARP0) {
-    // =========================== epilogue: one 64-column half of O of every chunk -> bf16 partial rows ===========================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-    const int w4 = warp & 3;
-    const int hlf = (warp - EPI_WARP0) >> 2;
-    const int r = (w4 << 5) | lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(w4 << 5) << 16;
-    const uint32_t tO = tmem + O_COL + hlf * 64 + lane_addr;
-    const bool issuer = (threadIdx.x & 127) == 0;             // first thread of this half's warpgroup
-    if (issuer) tma_prefetch_desc(&tm_o);
-    bool alive = true;
-    for (int c = 0; c < n_chunks; ++c) {
-      const RowMeta* meta = reinterpret_cast<const RowMeta*>(smem_gen + OFF_META) + (c & 3) * BM;
-      // staging: a 128-byte-swizzled [128 rows][128 B] tile per half, the layout a TMA tensor store
-      // reads (and conflict-free to write); two buffers, chunk parity
-      unsigned char* my_stage = smem_gen + OFF_STAGE + (c & 1) * TILE_BYTES + hlf * SUB_BYTES + r * 128;
-      if (r == 0) trace(4 + hlf, c, 0);
-      bool ok = mbar_wait(bar(META_FULL + (c & 3)), (c >> 2) & 1, abort_flag);
-      RowMeta mine = {0.f, 0.f};
-      if (ok) mine = meta[r];
-      if (ok) ok = mbar_wait(bar(O_FULL), c & 1, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        if (r == 0) trace(4 + hlf, c, 1);
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {                     // 32 columns at a time
-          uint32_t v[32];
-          tmem_ld32(tO + cc * 32, v);
-          tmem_wait_ld();
-          if (cc == 1) {                                      // this half of the TMEM buffer has been read
-            tc_fence_before();
-            mbar_arrive(bar(O_FREE));
+    int pv = 0, qk = 0;
+    uint32_t idle = 0;
+    bool v_ready = false;
+    while (alive && pv < n_chunks) {
+      bool did = false;
+      if (qk > pv) {                                          // S_pv has been issued
+        bool rdy = mbar_test(bar(P_FULL + pv % NSBUF), (pv / NSBUF) & 1);
+        if (rdy && pv > 0) rdy = mbar_test(bar(O_FREE), (pv - 1) & 1);
+        if (__any_sync(0xffffffffu, rdy)) {
+          if (!v_ready) { alive = mbar_wait(bar(V_FULL), 0, abort_flag); v_ready = true; if (!alive) break; }
+          // every lane observes the completed phases itself (returns at once): the issuing lane may
+          // not be one that saw them
+          alive = mbar_wait(bar(P_FULL + pv % NSBUF), (pv / NSBUF) & 1, abort_flag);
+          if (alive && pv > 0) alive = mbar_wait(bar(O_FREE), (pv - 1) & 1, abort_flag);
+          if (!alive) break;
+          tc_fence_after();
+          if (lane == 0) trace(3, pv, 4);
+          if (elect_one()) {
+            issue_pv(pv % NSBUF);
+            mma_commit(bar(O_FULL + pv % NSBUF));
           }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {                      // 16-byte pieces
-            uint4 o4;
-            o4.x = pack2<false>(__uint_as_float(v[q * 8]) * mine.inv, __uint_as_float(v[q * 8 + 1]) * mine.inv);
-            o4.y = pack2<false>(__uint_as_float(v[q * 8 + 2]) * mine.inv, __uint_as_float(v[q * 8 + 3]) * mine.inv);
-            o4.z = pack2<false>(__uint_as_float(v[q * 8 + 4]) * mine.inv, __uint_as_float(v[q * 8 + 5]) * mine.inv);
-            o4.w = pack2<false>(__uint_as_float(v[q * 8 + 6]) * mine.inv, __uint_as_float(v[q * 8 + 7]) * mine.inv);
-            *reinterpret_cast<uint4*>(my_stage + (((cc * 4 + q) ^ (r & 7)) << 4)) = o4;
-          }
+          __syncwarp();
+          if (lane == 0) trace(3, pv, 5);
+          ++pv;
+          did = true;
         }
       }
-      if (r == 0) trace(4 + hlf, c, 2);
-      const int64_t row0 = (static_cast<int64_t>(item.y) + static_cast<int64_t>(c) * tpc) * G;   // a multiple of 128
-      if (ok && hlf == 0) partial_lse[row0 + r] = mine.lse;
-      fence_proxy_async_smem();                               // generic-proxy writes -> read by the TMA store
-      // the store of chunk c - 1 has read its buffer before anybody passes this barrier, so chunk c + 1
-      // may overwrite it; the barrier also ANDs `ok`: nobody is left waiting at it after a timeout
-      if (issuer) tma_store_wait_read();
-      {
-        uint32_t out;
-        asm volatile("{\n\t.reg .pred pi, po;\n\tsetp.ne.u32 pi, %1, 0;\n\t"
-                     "bar.red.and.pred po, %2, 128, pi;\n\tselp.u32 %0, 1, 0, po;\n\t}"
-                     : "=r"(out) : "r"(static_cast<uint32_t>(ok)), "r"(1 + hlf) : "memory");
-        alive = out != 0;
+      if (qk < n_chunks && qk < pv + NSBUF) {
+        const int x = qk % NQBUF;
+        if (__any_sync(0xffffffffu, mbar_test(bar(Q_FULL + x), (qk / NQBUF) & 1))) {
+          alive = mbar_wait(bar(Q_FULL + x), (qk / NQBUF) & 1, abort_flag);
+          if (!alive) break;
+          tc_fence_after();
+          if (lane == 0) trace(3, qk, 2);
+          if (elect_one()) {
+            issue_qk(x, qk % NSBUF);
+            mma_commit(bar(S_FULL + qk % NSBUF));
+            mma_commit(bar(Q_EMPTY + x));
+          }
+          __syncwarp();
+          ++qk;
+          did = true;
+        }
       }
-      if (!alive) break;
-      if (issuer) {
-        tma_store_2d(&tm_o, smem_base + OFF_STAGE + (c & 1) * TILE_BYTES + hlf * SUB_BYTES, hlf * 64, static_cast<int>(row0));
-        tma_store_commit();
+      if (did) {
+        idle = 0;
+      } else if (++idle >= kSpinLimit) {
+        *abort_flag = 1;
+        alive = false;
+      } else if ((idle & 255u) == 255u && *abort_flag) {
+        alive = false;
       }
-      if (r == 0) trace(4 + hlf, c, 3);
     }
-    if (issuer) tma_store_wait_all();                         // shared memory stays valid until the stores are done
   } else {
-    // =========================== softmax ===========================
+    // =========================== softmax + epilogue: warpgroup x owns chunks c % 3 == x ===========================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
     const int x = warp >> 2;
     const int r = ((warp & 3) << 5) | lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
+    const uint32_t tS = tmem + x * BN + lane_addr;
+    const uint32_t tO = tmem + O_COL + lane_addr;
     const float scale_log2 = p.sm_scale * kLog2e * (p.k_scale_head ? p.k_scale_head[kvh] : 1.f);
     const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
+    // The partial rows of a token (its G heads, for one slot) are contiguous in the token-major buffer
+    // and in this warpgroup's staging tile: the first lane of every unit (G rows, at most the 32 rows
+    // of a warp) stores it with one bulk copy.  Everything after the TMEM reads is local to a warp --
+    // its 32 staging rows are written by its own lanes and stored by its own unit leaders -- so
+    // __syncwarp is all the ordering the epilogue needs.
+    const int unit_rows = G < 32 ? G : 32;
+    const bool issuer = (r & (unit_rows - 1)) == 0;
+    const int g = r & (G - 1);                                // head within the group
     bool alive = true;
+    unsigned char* my_stage = smem_gen + OFF_STAGE + x * TILE_BYTES + r * 256;
     int entry_next = (x < n_chunks && item.y + x * tpc + r / G < item.z) ? entries[item.y + x * tpc + r / G] : 0;
-    for (int c = x; c < n_chunks && alive; c += 2) {
+    for (int c = x; c < n_chunks && alive; c += NWG) {
+      const int u = c / NWG;
       const int e_idx = item.y + c * tpc + r / G;
       const bool row_ok = e_idx < item.z;
       const int entry = entry_next;
       {                                                       // prefetch the entry of this warpgroup's next chunk
-        const int e_nx = e_idx + 2 * tpc;
-        entry_next = (c + 2 < n_chunks && e_nx < item.z) ? entries[e_nx] : 0;
+        const int e_nx = e_idx + NWG * tpc;
+        entry_next = (c + NWG < n_chunks && e_nx < item.z) ? entries[e_nx] : 0;
       }
       const int tok = entry >> 5;
       const int lim = row_ok ? min(tok - qo_base + off, kv_len - 1) : -1;
       if (r == 0) trace(x, c, 0);
-      const int sb = c % NSBUF;
-      const uint32_t tS = tmem + sb * BN + lane_addr;
-      alive = mbar_wait(bar(S_FULL + sb), (c / NSBUF) & 1, abort_flag);
+      alive = mbar_wait(bar(S_FULL + x), u & 1, abort_flag);
       if (!alive) break;
       tc_fence_after();
       if (r == 0) trace(x, c, 1);
@@ -676,19 +648,52 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       f2_unpack(lsum2, l0, l1);
       const float l_sum = l0 + l1;
       if (r == 0) trace(x, c, 4);
-      // what the epilogue warpgroup needs for this row (4 buffers: chunk c + 4 cannot get this far
-      // before the epilogue of chunk c has read its entry)
-      RowMeta* meta = reinterpret_cast<RowMeta*>(smem_gen + OFF_META) + (c & 3) * BM;
-      RowMeta mine;
-      mine.inv = l_sum > 0.f ? vsh / l_sum : 0.f;
-      mine.lse = l_sum > 0.f ? msafe * kLn2 + __logf(l_sum) : -INFINITY;
-      meta[r] = mine;
-      mbar_arrive(bar(META_FULL + (c & 3)));
+      const float inv = l_sum > 0.f ? vsh / l_sum : 0.f;
+      const float lse = l_sum > 0.f ? msafe * kLn2 + __logf(l_sum) : -INFINITY;
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(P_FULL + sb));
+      mbar_arrive(bar(P_FULL + x));
       if (r == 0) trace(x, c, 2);
+
+      // ---- epilogue of the same chunk: O = P V (issued once P is in place and O of chunk c - 1 is drained) ----
+      // row of the partial buffer: [token][kv head][slot][head in group]
+      const int64_t prow = ((static_cast<int64_t>(tok) * p.num_kv_heads + kvh) * p.kv_block_num + (entry & 31)) * G + g;
+      if (row_ok) partial_lse[prow] = lse;
+      // the bulk copies of chunk c - 3 have left this warp's staging rows
+      if (issuer) tma_store_wait_read();
+      __syncwarp();
+      alive = mbar_wait(bar(O_FULL + x), u & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, alive)) { alive = false; break; }
+      tc_fence_after();
+      if (r == 0) trace(x, c, 5);
+      tmem_ld32(tO, sv[0]);
+      tmem_ld32(tO + 32, sv[1]);
+      tmem_ld32(tO + 64, sv[2]);
+      tmem_ld32(tO + 96, sv[3]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(O_FREE));                               // P_{c+1} V may overwrite O
+      if (r == 0) trace(x, c, 6);
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {                        // 16-byte pieces, XOR-swizzled by the head index
+          uint4 o4;
+          o4.x = pack2<false>(__uint_as_float(sv[cc][q * 8]) * inv, __uint_as_float(sv[cc][q * 8 + 1]) * inv);
+          o4.y = pack2<false>(__uint_as_float(sv[cc][q * 8 + 2]) * inv, __uint_as_float(sv[cc][q * 8 + 3]) * inv);
+          o4.z = pack2<false>(__uint_as_float(sv[cc][q * 8 + 4]) * inv, __uint_as_float(sv[cc][q * 8 + 5]) * inv);
+          o4.w = pack2<false>(__uint_as_float(sv[cc][q * 8 + 6]) * inv, __uint_as_float(sv[cc][q * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(my_stage + (((cc * 4 + q) ^ (g & 7)) << 4)) = o4;
+        }
+      fence_proxy_async_smem();                               // generic-proxy writes -> read by the bulk copy
+      __syncwarp();
+      if (issuer && row_ok) {
+        bulk_store(partial_o + prow * kHeadDim, smem_base + OFF_STAGE + x * TILE_BYTES + r * 256, unit_rows * 256);
+        tma_store_commit();
+      }
+      if (r == 0) trace(x, c, 7);
     }
+    if (issuer) tma_store_wait_all();                         // shared memory stays valid until the copies are done
   }
 
   // ---------------- teardown ----------------
@@ -715,7 +720,7 @@ int fmha_sparse_tc_supported(const MsaFmhaParams& p) {
   const int G = p.num_qo_heads / p.num_kv_heads;
   if (G < 1 || G > 128 || (128 % G) != 0 || p.kv_block_num > 32 || p.total_q >= (1 << 26)) return 0;
   // row indices of the partial buffer are int32 TMA coordinates
-  if ((static_cast<int64_t>(p.total_q) * p.kv_block_num + 128LL * p.num_logical_pages) * p.num_qo_heads > 0x7fffffffLL) return 0;
+  if (static_cast<int64_t>(p.total_q) * p.kv_block_num * p.num_qo_heads > 0x7fffffffLL) return 0;
   if (p.sparse_ws_bytes < fmha_sparse_tc_workspace_bytes(p.total_q, p.num_qo_heads, p.num_kv_heads, p.kv_block_num,
                                                          p.num_logical_pages))
     return 0;
@@ -750,14 +755,14 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   const unsigned n_blk_s = static_cast<unsigned>((p.total_q + 255) / 256) * p.num_kv_heads;
   auto index_pass = [&](bool scatter) {
     if (!smem_hist) {
-      if (scatter) sparse_index_kernel<true><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
-      else sparse_index_kernel<false><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+      if (scatter) sparse_index_kernel<true><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.vmask);
+      else sparse_index_kernel<false><<<n_blk, 256, 0, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.vmask);
     } else if (p.kv_block_num <= 16) {
-      if (scatter) sparse_index_smem_kernel<true, 16><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
-      else sparse_index_smem_kernel<false, 16><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+      if (scatter) sparse_index_smem_kernel<true, 16><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.vmask);
+      else sparse_index_smem_kernel<false, 16><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.vmask);
     } else {
-      if (scatter) sparse_index_smem_kernel<true, 32><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
-      else sparse_index_smem_kernel<false, 32><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.inv);
+      if (scatter) sparse_index_smem_kernel<true, 32><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.vmask);
+      else sparse_index_smem_kernel<false, 32><<<n_blk_s, 256, hist_bytes, stream>>>(ia, w.bin_count, w.bin_cursor, w.entries, w.vmask);
     }
   };
   index_pass(false);
@@ -768,7 +773,7 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   if (cudaGetLastError() != cudaSuccess) return MSA_ERR_LAUNCH;
 
   // 2. attention over (page, token chunk) items
-  CUtensorMap tq, tk, tv, to;
+  CUtensorMap tq, tk, tv;
   {
     if ((G & 7) == 0) {       // [token][half][head][64]: one box carries both halves of 8 rows
       const uint64_t dims[4] = {64, static_cast<uint64_t>(p.num_qo_heads), 2, static_cast<uint64_t>(p.total_q)};
@@ -781,11 +786,6 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
       const uint32_t box[3] = {64, static_cast<uint32_t>(G), 1};
       if (make_tma_map_bf16(&tq, p.q, 3, dims, str, box) != MSA_OK) return MSA_ERR_LAUNCH;
     }
-    // the partial rows: [cap * G][128], stored one 128-row chunk and 64-column half at a time
-    const uint64_t odims[2] = {128, static_cast<uint64_t>(w.cap) * G};
-    const uint64_t ostr[1] = {256};
-    const uint32_t obox[2] = {64, BM};
-    if (make_tma_map_bf16(&to, w.partial_o, 2, odims, ostr, obox) != MSA_OK) return MSA_ERR_LAUNCH;
     const uint64_t kd[4] = {128, BN, static_cast<uint64_t>(p.num_kv_heads), static_cast<uint64_t>(p.kv_extent)};
     const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * 2, static_cast<uint64_t>(p.k_stride_head) * 2,
                             static_cast<uint64_t>(p.k_stride_page) * 2};
@@ -799,12 +799,15 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 16 || !attr_done[dev]) {
+    // setmaxnreg can only hand out what the launch allocated: threads x compiled registers
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, sparse_tc_kernel) != cudaSuccess || fa.numRegs * NTHREADS < REGS_NEEDED) return MSA_ERR_LAUNCH;
     if (cudaFuncSetAttribute(sparse_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return MSA_ERR_LAUNCH;
     if (dev < 16) attr_done[dev] = true;
   }
-  sparse_tc_kernel<<<static_cast<unsigned>(w.max_items), NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv, to, w.items, w.part_start,
-                                                                                     -1, w.entries, w.partial_lse);
+  sparse_tc_kernel<<<static_cast<unsigned>(w.max_items), NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv, w.items, w.part_start, -1,
+                                                                                     w.entries, w.partial_lse, w.partial_o);
   if (cudaGetLastError() != cudaSuccess) return MSA_ERR_LAUNCH;
 
   // 3. merge the kv_block_num partials of every (token, head).  (Running the merge of kv head k on a
@@ -817,8 +820,8 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.out);
 #define MSA_MERGE(KK)                                                                                             \
   sparse_merge_kernel<KK><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                                    \
-      w.partial_o, w.partial_lse, w.inv, outp, p.lse, p.kv_block_num, p.total_q, p.num_qo_heads, p.num_kv_heads, \
-      p.out_stride_tok, p.out_stride_head, p.out_scale, 0, p.num_kv_heads)
+      w.partial_o, w.partial_lse, w.vmask, outp, p.lse, p.kv_block_num, p.total_q, p.num_qo_heads, p.num_kv_heads, \
+      p.out_stride_tok, p.out_stride_head, p.out_scale)
   if (p.kv_block_num <= 8) MSA_MERGE(8);
   else if (p.kv_block_num <= 16) MSA_MERGE(16);
   else MSA_MERGE(32);
