@@ -68,9 +68,9 @@ TRAFFIC = {
     "paged_prefill_b2_s4096_h32kv4": (111.5e6, "captured"),
     "paged_decode_b1_kv1048576_h64kv8": (4.33e9, "scaled x8 from the kv131072 capture (541.7 MB)"),
     "paged_decode_b1_kv131072_h64kv8": (541.7e6, "captured"),
-    "msa_prefill_b1_s8192_h32kv4_top16": (1.056e9, "captured (sparse_tc_kernel; sparse_merge_kernel: 1.032e9)"),
+    "msa_prefill_b1_s8192_h32kv4_top16": (1.055e9, "captured (sparse_tc_kernel; sparse_merge_kernel: 1.155e9)"),
     "msa_prefill_b2_s32768_h64kv8_top16": (16.9e9, "scaled x16 from the b1_s8192_h32kv4 capture (sparse_tc_kernel; "
-                                                    "sparse_merge_kernel: 16.5e9)"),
+                                                    "sparse_merge_kernel: 18.5e9)"),
     "msa_decode_e4m3_b8_kv131072_h64kv8_top16_split4": (138.1e6, "captured (score_gemv_kernel; decode_tc_kernel: 33.9e6)"),
     "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4": (552e6, "scaled x4 from the b8 capture (score_gemv_kernel; "
                                                                "decode_tc_kernel: 135e6)"),
