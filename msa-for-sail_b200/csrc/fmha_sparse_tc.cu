@@ -674,15 +674,19 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       tc_fence_before();
       mbar_arrive(bar(O_FREE));                               // P_{c+1} V may overwrite O
       if (r == 0) trace(x, c, 6);
+      const uint64_t inv2 = f2_pack(inv, inv), zero2 = f2_pack(0.f, 0.f);
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {                        // 16-byte pieces, XOR-swizzled by the head index
-          uint4 o4;
-          o4.x = pack2<false>(__uint_as_float(sv[cc][q * 8]) * inv, __uint_as_float(sv[cc][q * 8 + 1]) * inv);
-          o4.y = pack2<false>(__uint_as_float(sv[cc][q * 8 + 2]) * inv, __uint_as_float(sv[cc][q * 8 + 3]) * inv);
-          o4.z = pack2<false>(__uint_as_float(sv[cc][q * 8 + 4]) * inv, __uint_as_float(sv[cc][q * 8 + 5]) * inv);
-          o4.w = pack2<false>(__uint_as_float(sv[cc][q * 8 + 6]) * inv, __uint_as_float(sv[cc][q * 8 + 7]) * inv);
+          uint32_t o[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {                       // two columns per packed multiply
+            float a, b;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[cc][q * 8 + 2 * k]), __uint_as_float(sv[cc][q * 8 + 2 * k + 1])), inv2, zero2), a, b);
+            o[k] = pack2<false>(a, b);
+          }
+          const uint4 o4 = make_uint4(o[0], o[1], o[2], o[3]);
           *reinterpret_cast<uint4*>(my_stage + (((cc * 4 + q) ^ (g & 7)) << 4)) = o4;
         }
       fence_proxy_async_smem();                               // generic-proxy writes -> read by the bulk copy
