@@ -242,7 +242,7 @@ def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk):
                 stages=dict(proxy=(s_proxy, f_proxy, "TFLOP/s"),
                             topk=(s_topk, ms[:, :P].numel() * 4 + idx.numel() * 4, "GB/s"),
                             sparse=(s_sparse, f_sparse, "TFLOP/s")),
-                metric="msa_prefill_effective_tflops", unit="TFLOP/s", bound="tensor", launches=9, graph=False,
+                metric="msa_prefill_effective_tflops", unit="TFLOP/s", bound="tensor", launches=7, graph=False,
                 h2d=q_h.numel() * 2, d2h=out_h.numel() * 2,
                 l2="inputs larger than L2 (Q+O = %.2f GB per GPU); the KV cache stays resident" % (
                     2 * q.numel() * 2 / 1e9),
