@@ -148,8 +148,12 @@ def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk):
     q_h = (torch.randn(b * ql, hq, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
     k_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
     v_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
-    # every sequence owns a slab of P pages and a shuffled page table over it
-    local = torch.stack([torch.randperm(P, generator=g) for _ in range(b)]).to(torch.int32)
+    # every sequence owns a slab of P pages; its page table is shuffled within groups of P / NCH pages, so
+    # that the pages of the first j row chunks of a sequence are the first j groups of its slab
+    NCH = 4 if (ql == kl and P % 4 == 0 and ql % (4 * 256) == 0) else 1     # row chunks per sequence (end to end)
+    gp = P // NCH
+    local = torch.stack([torch.cat([torch.randperm(gp, generator=g) + j * gp for j in range(NCH)])
+                         for _ in range(b)]).to(torch.int32)
     table = (local + torch.arange(b, dtype=torch.int32).view(b, 1) * P).reshape(-1).to(dev)
     q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     plan = msa.fmha_sail_plan(_i32([ql] * b), _i32([kl] * b), hq, num_kv_heads=hk, page_size=PAGE)
@@ -160,36 +164,43 @@ def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk):
     def step():
         msa.fmha_sail(q, k, v, plan, kv_indices=table, out=out, lse=lse)
 
-    # end to end: the inputs of a step start in pinned host memory.  One public-API call per sequence,
-    # so that the copy-in of sequence i + 1, the attention of sequence i and the copy-out of sequence
-    # i - 1 overlap (three streams; every byte of Q, K, V still crosses PCIe inside the timed region).
-    plan1 = msa.fmha_sail_plan(_i32([ql]), _i32([kl]), hq, num_kv_heads=hk, page_size=PAGE)
+    # end to end: the inputs of a step start in pinned host memory.  One public-API call per row chunk of
+    # a sequence (chunked prefill: chunk j attends to the keys of chunks 0..j, whose pages are the first
+    # j + 1 groups of the slab), so that the copy-in of the next chunk, the attention of this one and the
+    # copy-out of the previous one overlap (three streams; every byte of Q, K, V still crosses PCIe
+    # inside the timed region, every byte of O comes back).
+    cq = ql // NCH
+    plans = [msa.fmha_sail_plan(_i32([cq]), _i32([(j + 1) * cq]), hq, num_kv_heads=hk, page_size=PAGE) for j in range(NCH)]
     local_dev = local.to(dev)
     qd, kd, vd, od = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(out)
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    ev_in = [torch.cuda.Event() for _ in range(b)]
-    ev_done = [torch.cuda.Event() for _ in range(b)]
+    ev_in = [torch.cuda.Event() for _ in range(b * NCH)]
+    ev_done = [torch.cuda.Event() for _ in range(b * NCH)]
 
     def e2e_step():
         cur = torch.cuda.current_stream()
         s_in.wait_stream(cur); s_out.wait_stream(cur)          # the previous step has released the buffers
         for i in range(b):
-            rq, rk = slice(i * ql, (i + 1) * ql), slice(i * P, (i + 1) * P)
-            with torch.cuda.stream(s_in):
-                qd[rq].copy_(q_h[rq], non_blocking=True)
-                kd[rk].copy_(k_h[rk], non_blocking=True)
-                vd[rk].copy_(v_h[rk], non_blocking=True)
-                ev_in[i].record(s_in)
-            cur.wait_event(ev_in[i])
-            msa.fmha_sail(qd[rq], kd[rk], vd[rk], plan1, kv_indices=local_dev[i], out=od[rq])
-            ev_done[i].record(cur)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_done[i])
-                out_h[rq].copy_(od[rq], non_blocking=True)
+            rk = slice(i * P, (i + 1) * P)
+            for j in range(NCH):
+                n = i * NCH + j
+                rq = slice(i * ql + j * cq, i * ql + (j + 1) * cq)
+                rp = slice(i * P + j * gp, i * P + (j + 1) * gp)
+                with torch.cuda.stream(s_in):
+                    qd[rq].copy_(q_h[rq], non_blocking=True)
+                    kd[rp].copy_(k_h[rp], non_blocking=True)
+                    vd[rp].copy_(v_h[rp], non_blocking=True)
+                    ev_in[n].record(s_in)
+                cur.wait_event(ev_in[n])
+                msa.fmha_sail(qd[rq], kd[rk], vd[rk], plans[j], kv_indices=local_dev[i, :(j + 1) * gp], out=od[rq])
+                ev_done[n].record(cur)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[n])
+                    out_h[rq].copy_(od[rq], non_blocking=True)
         cur.wait_stream(s_out)
 
     nbytes = (q.numel() + k.numel() + v.numel() + out.numel()) * 2
-    return dict(step=step, e2e_step=e2e_step, flops=attention_flops(b, ql, kl, hq), bytes=nbytes,
+    return dict(step=step, e2e_step=e2e_step, flops=attention_flops(b, ql, kl, hq), bytes=nbytes, results=(out, out_h),
                 metric="prefill_effective_tflops", unit="TFLOP/s", bound="tensor", launches=1, graph=False,
                 h2d=(q_h.numel() + k_h.numel() + v_h.numel()) * 2, d2h=out_h.numel() * 2,
                 l2="inputs larger than L2 (Q+K+V+O = %.2f GB per GPU)" % (nbytes / 1e9),
@@ -568,8 +579,9 @@ def main():
             e2e_ms = float(t.item())
         e2e = {"value": world * work / (e2e_ms * 1e-3), "unit": wl["unit"], "h2d_bytes_per_step": wl["h2d"],
                "d2h_bytes_per_step": wl["d2h"], "ms_per_step": e2e_ms, "steps": n_e2e,
-               "note": ("one public API call per sequence; the copy-in of a sequence's Q/K/V from pinned host memory, its "
-                        "attention and the copy-out of its O overlap with the neighbouring sequences on three streams"
+               "note": ("chunked prefill through the public API, four row chunks per sequence; the copy-in of a chunk's Q "
+                        "rows and K/V pages from pinned host memory, its attention and the copy-out of its O overlap "
+                        "with the neighbouring chunks on three streams"
                         if kind == "prefill" else
                         "public API call with pinned host tensors copied in and the result copied out each step; "
                         "the KV cache is device-resident state")}
