@@ -30,3 +30,21 @@ def test_prefill_end_to_end_step_matches_the_resident_step():
     assert (got - ref).abs().max().item() <= 2e-2
     cos = torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item()
     assert cos >= 0.9999
+
+
+def test_msa_prefill_end_to_end_step_matches_the_resident_step():
+    """Chunked sparse prefill (row chunks with growing kv_len) selects the same pages and gives the
+    same output as the whole sequence in one call."""
+    import bench
+    import msa_for_sail as msa
+    dev = torch.device("cuda:0")
+    wl = bench.setup_msa_prefill(msa, dev, 11, b=2, t=8192, hq=16, hk=2, topk=8)
+    wl["step"]()
+    wl["e2e_step"]()
+    wl["e2e_step"]()
+    torch.cuda.synchronize()
+    out, out_h = wl["results"]
+    ref, got = out.float().cpu(), out_h.float()
+    assert torch.isfinite(got).all()
+    assert (got - ref).abs().max().item() <= 2e-2
+    assert torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item() >= 0.9999
