@@ -177,7 +177,8 @@ int msa_plan_dense(const MsaPlanArgs* args, MsaWorkItem* work, int32_t capacity,
  * kv_len_out, qo_offset_out (causal: kv_len - qo_len where qo_offset_in is NULL or
  * negative; non-causal: `noncausal_offset`), kv_page_indptr ([batch + 1], pages of
  * `page_size` keys, NULL for ragged K/V), token_batch ([max_total_q], NULL when unused),
- * splits_per_row ([max_total_q], = num_splits) and the work list: exactly
+ * splits_per_row ([max_total_q]: num_splits for real tokens, 0 for the padding past the last
+ * one, so that a merge over max_total_q rows writes zeros there) and the work list: exactly
  * batch * row_tiles * (num_qo_heads / pack) * num_splits items, item
  * (((b * row_tiles + r) * groups) + g) * S + s = row tile (row_tiles - 1 - r) of batch item b
  * (later rows first: under a causal mask they see more keys), head group g, the s-th of S
@@ -212,10 +213,15 @@ int msa_plan_device(const MsaPlanDeviceArgs* args, msa_stream_t stream);
  * workspace, api.py:141-167).  It exists for embedders that may not allocate device
  * memory at call time -- an engine whose memory pool owns the whole device after
  * start-up, a sandboxed plugin host that passes tensors but no allocator.  Same
- * arguments as msa_fmha_fwd (dense or sparse, MSA_FLAG_OUT_O only, block_m 16/64/128)
- * with partial_o / partial_lse left NULL and num_splits = the S of the work list;
- * the result goes to params->out (and params->lse).  The call performs no
- * cudaMalloc / cudaFree and calls no allocating routine.
+ * arguments and the same argument checks as msa_fmha_fwd (dense or sparse, MSA_FLAG_OUT_O
+ * only, block_m 16/64/128) with partial_o / partial_lse left NULL and num_splits = the S of
+ * the work list; the result goes to params->out (and params->lse).  `splits_per_row`
+ * ([total_q] device int32, or NULL) has the meaning it has in msa_lse_merge: how many of
+ * the S slots of a token the merge looks at; NULL = all S.  Either way a slot that no work
+ * item of this call wrote counts as empty: the call first marks every slot as empty (LSE
+ * -inf), so a short or empty work list gives zeros / -inf LSE, never a value left behind by
+ * an earlier call.  The call performs no cudaMalloc / cudaFree and calls no allocating
+ * routine.
  *  - Limit: num_splits * total_q * num_qo_heads <= MSA_STATIC_SCRATCH_MAX_ROWS,
  *    otherwise MSA_ERR_TOO_LARGE.  The array (about 8.5 MB) is resident on every GPU
  *    that loads the library, until the process exits.

@@ -17,21 +17,30 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int64_t fmha_sparse_tc_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
 }  // namespace msa
 
-extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
-  if (!pp) return MSA_ERR_BAD_ARG;
-  const MsaFmhaParams& p = *pp;
+namespace msa {
+// Argument checks shared by every entry point that takes MsaFmhaParams.  Nothing here touches the
+// device.  `own_scratch`: the split workspace is supplied by the library after this check
+// (msa_fmha_fwd_split_static), so partial_o / partial_lse are expected to be NULL.
+int validate_fmha(const MsaFmhaParams& p, bool own_scratch) {
   const bool sparse = (p.flags & MSA_FLAG_SPARSE) != 0;
   const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;
   const bool has_s = (p.flags & MSA_FLAG_OUT_SCORE) != 0;
   if (!has_o && !has_s) return MSA_ERR_BAD_ARG;
   if (!p.q || !p.k || !p.qo_start || !p.kv_len || !p.qo_offset) return MSA_ERR_BAD_ARG;
+  if (p.total_q < 0 || p.batch < 0) return MSA_ERR_BAD_ARG;
   if (has_o && (!p.v || (!p.out && !p.partial_o))) return MSA_ERR_BAD_ARG;
   if (has_s && (!p.max_score || p.max_k_tiles <= 0)) return MSA_ERR_BAD_ARG;
-  if (p.partial_o && (!p.partial_lse || p.num_splits < 1)) return MSA_ERR_BAD_ARG;
-  if (!p.partial_o && p.num_splits != 1) return MSA_ERR_BAD_ARG;
+  if (own_scratch) {
+    if (p.partial_o || p.partial_lse || p.num_splits < 1) return MSA_ERR_BAD_ARG;
+  } else {
+    if (p.partial_o && (!p.partial_lse || p.num_splits < 1)) return MSA_ERR_BAD_ARG;
+    if (!p.partial_o && p.num_splits != 1) return MSA_ERR_BAD_ARG;
+  }
   if (p.num_qo_heads <= 0 || p.num_kv_heads <= 0 || p.num_qo_heads % p.num_kv_heads) return MSA_ERR_BAD_ARG;
   const int h_r = p.num_qo_heads / p.num_kv_heads;
   if (p.pack < 1 || h_r % p.pack) return MSA_ERR_BAD_ARG;
+  if (p.block_m != 16 && p.block_m != 64 && p.block_m != 128 && p.block_m != 256) return MSA_ERR_BAD_ARG;
+  if (p.pack > p.block_m) return MSA_ERR_BAD_ARG;                 // rows of one token never straddle two items
   if (p.page_size > 0 && (!p.kv_page_indptr || !p.kv_indices)) return MSA_ERR_BAD_ARG;
   if (p.page_size <= 0 && !p.kv_start) return MSA_ERR_BAD_ARG;
   if (p.q_dtype != MSA_DT_BF16 && p.q_dtype != MSA_DT_E4M3) return MSA_ERR_UNSUPPORTED;
@@ -41,9 +50,9 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
     if (!p.kv_block_indexes || !p.token_batch || p.kv_block_num <= 0) return MSA_ERR_BAD_ARG;
     if (p.page_size != msa::kKvTile) return MSA_ERR_UNSUPPORTED;   // a selected block is one 128-key page
     if (has_s) return MSA_ERR_UNSUPPORTED;
-    if (p.pack != h_r || p.pack > p.block_m) return MSA_ERR_BAD_ARG;
+    if (p.pack != h_r) return MSA_ERR_BAD_ARG;
   } else {
-    if (p.num_work > 0 && !p.work) return MSA_ERR_BAD_ARG;
+    if (p.num_work < 0 || (p.num_work > 0 && !p.work)) return MSA_ERR_BAD_ARG;
   }
   // 16-byte alignment of every row the kernels touch with vector accesses
   const int qe = p.q_dtype == MSA_DT_E4M3 ? 1 : 2, ke = p.kv_dtype == MSA_DT_E4M3 ? 1 : 2;
@@ -53,7 +62,14 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
   if ((p.k_stride_tok * ke) % 16 || (p.k_stride_head * ke) % 16 || (p.k_stride_page * ke) % 16) return MSA_ERR_BAD_ARG;
   if (has_o && ((p.v_stride_tok * ke) % 16 || (p.v_stride_head * ke) % 16 || (p.v_stride_page * ke) % 16)) return MSA_ERR_BAD_ARG;
   if (p.out && ((p.out_stride_tok * 2) % 16 || (p.out_stride_head * 2) % 16)) return MSA_ERR_BAD_ARG;
+  return MSA_OK;
+}
+}  // namespace msa
 
+extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
+  if (!pp) return MSA_ERR_BAD_ARG;
+  const MsaFmhaParams& p = *pp;
+  if (const int rc = msa::validate_fmha(p, false)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (msa::fmha_sparse_tc_supported(p)) return msa::fmha_sparse_tc_launch(p, stream);
   if (msa::score_gemv_supported(p)) return msa::score_gemv_launch(p, stream);

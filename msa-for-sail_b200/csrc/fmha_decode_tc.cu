@@ -8,13 +8,16 @@
 // A decode step reads every selected K/V byte once and does ~16 FLOP per byte, so what matters
 // is keeping loads in flight.  One CTA = one (batch item | token, KV head, split).  Its rows are
 // the packed (token, head-in-group) pairs; they occupy the first lanes of a 128-row MMA tile (the
-// idle rows cost tensor time that is not on the critical path).  K and V pages stream through
-// 3-deep TMA rings (192 KB in flight per SM); no thread ever computes a load address.
+// idle rows cost tensor time that is not on the critical path).  K and V pages stream through TMA
+// rings of their own (3 tiles deep for bf16, 6 half-page tiles for e4m3); no thread ever computes
+// a load address.
 //
-//   warps 0-3   softmax: only the warps that own real rows take part; thread r owns row r
-//   warp 4      TMA producer (page id read from the page table / the selected-page list)
+//   warps 0-3   softmax: thread r owns row r; with at most 16 rows (QUAD) the rows are replicated
+//               into the four 32-lane quadrants and warp w handles key columns [32 w, 32 w + 32)
+//   warp 4      TMA producer of K (page id read from the page table / the selected-page list)
 //   warp 5      MMA issuer: S[j & 1] = Q K_j^T, O += P_j V_j; S is double-buffered in TMEM so
 //               QK of tile j + 1 overlaps the softmax of tile j
+//   warp 6      TMA producer of V (its own ring, so a full V ring never delays the next K tile)
 //
 // Output: normalised partial O (fp32) + natural-log LSE per split, or the final bf16 O when the
 // work item is unsplit.  Every wait is bounded (tc_ptx.cuh).
@@ -45,6 +48,7 @@ constexpr int STAGE_LD = kHeadDim + 4;          // floats per staged O row (padd
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 7, V_FULL = 13, V_EMPTY = 19, S_FULL = 25, P_FULL = 27, PV_DONE = 29,
            V_FIX = 30, NUM_BARS = 31 };
 
+#ifdef MSA_DEBUG_HOOKS
 // diagnostic timeline: when set, every CTA records 16 words (see msa_debug_decode_trace)
 __device__ unsigned long long* g_trace = nullptr;
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -52,6 +56,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+#endif
 
 // Shared / tensor memory plan of one instantiation.
 //   F8    K/V (and Q, P) are e4m3 and the MMAs are kind::f8f6f4; otherwise bf16 and kind::f16.
@@ -117,9 +122,14 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   constexpr float kRescaleThreshold = F8 ? 4.0f : 8.0f;
   constexpr float kPOffset = F8 ? 4.0f : 0.0f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef MSA_DEBUG_HOOKS
   unsigned long long* trace = (threadIdx.x == 0 && g_trace) ? g_trace + 16ull * blockIdx.x : nullptr;
   const long long clk0 = clock64();
   if (trace) { trace[0] = global_ns(); unsigned id; asm("mov.u32 %0, %%smid;" : "=r"(id)); trace[2] = id; }
+#else
+  constexpr unsigned long long* trace = nullptr;   // the `if (trace)` records below compile to nothing
+  constexpr long long clk0 = 0;
+#endif
   const bool sparse = (p.flags & MSA_FLAG_SPARSE) != 0;
   const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;   // false: score-only pass (no V, no P, no O)
   const int G = p.pack;
@@ -749,7 +759,9 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (*abort_flag && threadIdx.x == 0 && p.status) atomicExch(p.status, MSA_STATUS_TIMEOUT);
+#ifdef MSA_DEBUG_HOOKS
   if (trace) { trace[13] = clock64() - clk0; trace[1] = global_ns(); }
+#endif
   if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, C::TMEM_COLS);
@@ -862,13 +874,16 @@ int fmha_decode_tc_occupancy(int f8, int quad) {
 
 }  // namespace msa
 
-// diagnostic, not part of the documented ABI: resident CTAs per SM of a decode-kernel variant
+#ifdef MSA_DEBUG_HOOKS
+// Diagnostics of builds with -DMSA_DEBUG_HOOKS only.
+// resident CTAs per SM of a decode-kernel variant
 extern "C" int msa_debug_decode_occupancy(int f8, int quad) { return msa::fmha_decode_tc_occupancy(f8, quad); }
 
-// diagnostic, not part of the documented ABI: device buffer of 16 x uint64 per CTA, or NULL to stop
+// device buffer of 16 x uint64 per CTA, or NULL to stop
 // [0] start ns  [1] end ns  [2] SM id; clocks since entry: [3] prologue done, [4..7], [14], [15] steps of
 // tile 12 / 13 in the softmax (S ready, loaded, max done, P stored, S of 13 ready, P_FULL arrived), [8] last P written, [9] last P.V done, [10] O staged, [11] staging barrier passed,
 // [12] rows combined and stored, [13] exit
 extern "C" void msa_debug_decode_trace(unsigned long long* device_buf) {
   cudaMemcpyToSymbol(msa::decode_tc::g_trace, &device_buf, sizeof(device_buf));
 }
+#endif

@@ -17,12 +17,12 @@
 // Every (token, page) pair is computed exactly once regardless of how the selections overlap.
 //
 // Kernels in this file: count / scan / scatter (counting sort of the selections by page), the merge and the
-// attention kernel.  Roles of the attention kernel (20 warps): warps 0-3 / 4-7 softmax of even / odd
-// chunks (152 registers each: a whole row of S is held at once); warps 8-11 / 12-15 epilogue of
-// head_dim [0, 64) / [64, 128) (O out of TMEM, bf16, shared memory, one TMA tensor store per token
-// and half, overlapping the softmax of later chunks); warps 16-18 loaders (the page by TMA, once;
-// the Q rows of a chunk gathered with one TMA box per 8 rows, the boxes spread over the lanes of
-// three warps because a warp issues its lanes' boxes one after another); warp 19 MMA issuer.
+// attention kernel.  Roles of the attention kernel (16 warps): warpgroups 0-2 (warps 0-11, 152 registers
+// each) own every third chunk from S to the stored partial -- softmax of the chunk (a whole row of S is
+// held at once), then, once P V is done, O out of TMEM, normalised, bf16, staged in shared memory and
+// stored with one bulk copy per token; warps 12-14 loaders (the page by TMA, once; the Q rows of a chunk
+// gathered with one TMA box per 8 rows, the boxes spread over the lanes of three warps because a warp
+// issues its lanes' boxes one after another); warp 15 MMA issuer.
 // All waits are bounded (see tc_ptx.cuh).
 #include "tc_ptx.cuh"
 
@@ -72,13 +72,12 @@ constexpr uint32_t O_COL = NSBUF * BN;
 enum Bar { K_FULL = 0, V_FULL = 1, V_FIX = 2, Q_FULL = 3, Q_EMPTY = 5, S_FULL = 7, P_FULL = 10, O_FULL = 13,
            O_FREE = 16, NUM_BARS = 17 };
 
-// test hook: take the global-atomics index kernels even when the histogram fits shared memory
-bool g_force_global_index = false;
-
+#ifdef MSA_DEBUG_HOOKS
 // optional clock trace of one CTA (debugging aid): [6 roles][512 chunks][8 tags]; roles: warpgroups 0-2,
 // MMA 3, loaders 4
 __device__ unsigned long long g_trace[6 * 512 * 8];
 __device__ int g_trace_cta = -1;
+#endif
 
 struct Ws {                 // device workspace carved by carve()
   int32_t* bin_count;       // [NB + 1]
@@ -342,10 +341,14 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   volatile int* skip_flag = abort_flag + 1;      // set when the status word already reports a timeout
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef MSA_DEBUG_HOOKS
   const bool tracing = static_cast<int>(blockIdx.x) == g_trace_cta;
   auto trace = [&](int role, int c, int tag) {
     if (tracing && c < 512) g_trace[(role * 512 + c) * 8 + tag] = clock64();
   };
+#else
+  auto trace = [](int, int, int) {};              // compiles to nothing
+#endif
 
   // ---------------- work item ----------------
   const int4 item = items[item_idx];
@@ -755,7 +758,7 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   const int tpc = BM / G;
   const int rows_per_item = tpc * ITEM_CHUNKS;
   const size_t hist_bytes = static_cast<size_t>(NP) * 4;
-  const bool smem_hist = hist_bytes <= 48 * 1024 && !g_force_global_index;
+  const bool smem_hist = hist_bytes <= 48 * 1024;
   const unsigned n_blk_s = static_cast<unsigned>((p.total_q + 255) / 256) * p.num_kv_heads;
   auto index_pass = [&](bool scatter) {
     if (!smem_hist) {
@@ -835,13 +838,13 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 
 }  // namespace msa
 
-// Test hook (not part of the documented ABI): exercise the index kernels that large page counts use.
-extern "C" void msa_debug_sparse_force_global_index(int on) { msa::sparse_tc::g_force_global_index = on != 0; }
-
-// Debug aid: choose the CTA whose phase clocks are recorded (-1 = none) / read the record back.
+#ifdef MSA_DEBUG_HOOKS
+// Debug aid (builds with -DMSA_DEBUG_HOOKS only): choose the CTA whose phase clocks are recorded
+// (-1 = none) / read the record back.
 extern "C" void msa_debug_sparse_trace_cta(int cta) {
   cudaMemcpyToSymbol(msa::sparse_tc::g_trace_cta, &cta, sizeof(int));
 }
 extern "C" void msa_debug_sparse_trace_read(unsigned long long* host_buf) {
   cudaMemcpyFromSymbol(host_buf, msa::sparse_tc::g_trace, sizeof(unsigned long long) * 6 * 512 * 8);
 }
+#endif

@@ -50,9 +50,8 @@ constexpr uint32_t kEmuMask = 0x5252;              // pairs (of 16 per 32 column
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13,
            V_FIX = 15, NUM_BARS = 16 };
 
-struct Knobs {            // descriptor constants (bytes) + optional per-phase clock trace
-  uint32_t k_lbo, k_sbo, v_lbo, v_sbo, v_kstep, p_colstep;
-  unsigned long long* trace;   // [4 roles][512 tiles][8 tags] clock64 samples of one CTA, or null
+struct Knobs {            // per-phase clock trace of one CTA (read only in builds with -DMSA_DEBUG_HOOKS)
+  unsigned long long* trace;   // [4 roles][512 tiles][8 tags] clock64 samples, or null
   int trace_cta;
 };
 
@@ -70,7 +69,11 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   auto bar = [&](int i) -> uint32_t { return bars + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef MSA_DEBUG_HOOKS
   const bool tracing = kn.trace != nullptr && static_cast<int>(blockIdx.x) == kn.trace_cta;
+#else
+  constexpr bool tracing = false;                 // the trace calls below compile to nothing
+#endif
   auto trace = [&](int role, int j, int tag) {
     if (tracing && j < 512) kn.trace[(role * 512 + j) * 8 + tag] = clock64();
   };
@@ -481,7 +484,7 @@ bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-Knobs g_knobs = {16, 1024, 16384, 1024, 2048, 8, nullptr, 0};
+Knobs g_knobs = {nullptr, 0};
 
 }  // namespace
 
@@ -552,13 +555,10 @@ int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 
 }  // namespace msa
 
-// Debug hook while the descriptor constants are being validated on hardware.
-extern "C" void msa_debug_tc_knobs(uint32_t k_lbo, uint32_t k_sbo, uint32_t v_lbo, uint32_t v_sbo, uint32_t v_kstep,
-                                   uint32_t p_colstep) {
-  msa::tc::g_knobs.k_lbo = k_lbo; msa::tc::g_knobs.k_sbo = k_sbo; msa::tc::g_knobs.v_lbo = v_lbo;
-  msa::tc::g_knobs.v_sbo = v_sbo; msa::tc::g_knobs.v_kstep = v_kstep; msa::tc::g_knobs.p_colstep = p_colstep;
-}
+#ifdef MSA_DEBUG_HOOKS
+// Debug aid (builds with -DMSA_DEBUG_HOOKS only): record the phase clocks of one CTA into `buf`.
 extern "C" void msa_debug_tc_trace(unsigned long long* buf, int cta) {
   msa::tc::g_knobs.trace = buf;
   msa::tc::g_knobs.trace_cta = cta;
 }
+#endif

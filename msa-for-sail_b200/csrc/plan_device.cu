@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) plan_device_kernel(const MsaPlanDeviceArg
   // per-token arrays
   const int total_q = s_total_q;
   for (int t = threadIdx.x; t < a.max_total_q; t += blockDim.x) {
-    if (a.splits_per_row) a.splits_per_row[t] = S;
+    if (a.splits_per_row) a.splits_per_row[t] = t < total_q ? S : 0;   // padded rows merge to 0 / LSE -inf
     if (a.token_batch) {
       int b = 0;
       if (t < total_q && a.qo_start) {                     // last b with qo_start[b] <= t (binary search)

@@ -68,7 +68,9 @@ score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
   const int h_r = p.num_qo_heads / p.num_kv_heads;
   const int kvh = head0 / h_r, G = p.pack;
   const int qo_base = p.qo_start[b];
-  const int nrows = (p.qo_start[b + 1] - qo_base) * G;
+  // rows of this item; a batch slot without query tokens (graph-safe padding) is an empty item
+  const int nrows = min((p.qo_start[b + 1] - qo_base) * G, w.num_rows);
+  if (nrows <= 0) return;                          // uniform for the CTA; nothing below is shared
   const int kv_len = p.kv_len[b], off = p.qo_offset[b], page_base = p.kv_page_indptr[b];
   const int c = lane % L, ksub = lane / L;
 

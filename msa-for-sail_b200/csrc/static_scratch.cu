@@ -11,6 +11,7 @@
 
 namespace msa {
 int fmha_mma_launch(const MsaFmhaParams& p, cudaStream_t stream);
+int validate_fmha(const MsaFmhaParams& p, bool own_scratch);
 
 namespace {
 
@@ -20,8 +21,17 @@ constexpr long long kFloatsPerRow = kHeadDim + 1;
 
 static __device__ __align__(256) float g_split_scratch[kMaxRows * kFloatsPerRow];
 
+// Marks every (split, token, head) slot as "not computed": the merge gives a slot whose LSE is -inf
+// the weight 0 and never reads its partial O.
+__global__ void __launch_bounds__(256) clear_lse_kernel(float* __restrict__ lse, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lse[i] = -INFINITY;
+}
+
 // Device address of g_split_scratch on the given device, resolved on first use there.  In host
-// code the symbol's name is only a handle, never a pointer a kernel could use.
+// code the symbol's name is only a handle, never a pointer a kernel could use.  The cache is
+// written without a lock: two threads that race on a device's first call both store the same
+// address (the lookup is idempotent), so the worst case is one redundant lookup.
 float* scratch_address(int device, cudaError_t* err) {
   static float* addr[64] = {};
   *err = cudaSuccess;
@@ -43,10 +53,10 @@ extern "C" int msa_fmha_fwd_split_static(const MsaFmhaParams* pp, const int32_t*
   using namespace msa;
   if (!pp) return MSA_ERR_BAD_ARG;
   MsaFmhaParams p = *pp;
-  if (p.partial_o || p.partial_lse) return MSA_ERR_BAD_ARG;      // the scratch is ours
+  // the same argument checks as msa_fmha_fwd, before anything touches the device
   if (!(p.flags & MSA_FLAG_OUT_O) || (p.flags & MSA_FLAG_OUT_SCORE) || !p.out) return MSA_ERR_BAD_ARG;
-  if (p.num_splits < 1 || p.total_q < 0 || p.num_qo_heads <= 0) return MSA_ERR_BAD_ARG;
-  if (p.block_m != 16 && p.block_m != 64 && p.block_m != 128) return MSA_ERR_UNSUPPORTED;
+  if (const int rc = validate_fmha(p, true)) return rc;
+  if (p.block_m == 256) return MSA_ERR_UNSUPPORTED;              // 256-row items belong to the unsplit prefill kernel
   const long long rows = static_cast<long long>(p.num_splits) * p.total_q * p.num_qo_heads;
   if (rows > kMaxRows) return MSA_ERR_TOO_LARGE;
   if (rows == 0) return MSA_OK;
@@ -57,14 +67,18 @@ extern "C" int msa_fmha_fwd_split_static(const MsaFmhaParams* pp, const int32_t*
   float* scratch = scratch_address(device, &err);
   if (!scratch) return MSA_ERR_LAUNCH;
 
-  // Every (split, token, head) row below splits_per_row is written by the forward kernel
-  // before the merge reads it, so nothing left over from an earlier call is ever consumed and
-  // nothing has to be cleared.
+  // The array keeps what the previous call left in it, and a work list need not cover every slot
+  // (an empty list; a row tile whose keys gave fewer than num_splits items when splits_per_row is
+  // NULL).  So every LSE slot of this call starts at -inf: a slot that no work item writes merges
+  // with weight 0 instead of with a stale partial.
   float* user_lse = p.lse;
   p.partial_o = scratch;
   p.partial_lse = scratch + rows * kHeadDim;
   p.lse = nullptr;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int n_lse = static_cast<int>(rows);
+  clear_lse_kernel<<<(n_lse + 255) / 256, 256, 0, stream>>>(p.partial_lse, n_lse);
+  if (cudaGetLastError() != cudaSuccess) return MSA_ERR_LAUNCH;
   const int rc = fmha_mma_launch(p, stream);
   if (rc != MSA_OK) return rc;
   return msa_lse_merge(p.partial_o, MSA_DT_F32, p.partial_lse, splits_per_row, p.out, user_lse, p.num_splits, p.total_q,

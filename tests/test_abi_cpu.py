@@ -129,3 +129,82 @@ def test_api_surface_matches_upstream_names():
     assert list(sig.parameters) == ["batch_size", "num_qo_heads", "num_kv_heads", "max_qo_len", "page_size",
                                     "kv_block_num", "num_kv_splits", "device", "output_maxscore",
                                     "use_fp8_kvcache"]
+
+
+def _valid_params(L):
+    """A well-formed ragged dense call whose pointers are fake but aligned: every check below
+    fails on the argument it breaks, before anything would touch the device."""
+    p = L.MsaFmhaParams()
+    fake = 0x1000
+    for f in ("q", "k", "v", "out", "qo_start", "kv_start", "kv_len", "qo_offset", "work"):
+        setattr(p, f, fake)
+    p.q_stride_tok, p.q_stride_head = 8 * 128, 128
+    p.k_stride_tok = p.v_stride_tok = 2 * 128
+    p.k_stride_head = p.v_stride_head = 128
+    p.out_stride_tok, p.out_stride_head = 8 * 128, 128
+    p.total_q, p.num_qo_heads, p.num_kv_heads, p.batch = 4, 8, 2, 1
+    p.num_work, p.block_m, p.pack, p.page_size, p.num_splits = 1, 16, 4, 0, 1
+    p.q_dtype = p.kv_dtype = L.MSA_DT_BF16
+    p.flags = L.FLAG_OUT_O
+    p.sm_scale, p.out_scale = 0.1, 1.0
+    return p
+
+
+BROKEN = [
+    ("kv_len", None, -1), ("q", None, -1), ("qo_offset", None, -1), ("v", None, -1),
+    ("pack", 0, -1), ("pack", 3, -1), ("num_kv_heads", 0, -1), ("num_kv_heads", 3, -1),
+    ("block_m", 48, -1), ("out_stride_tok", 8 * 128 + 4, -1), ("q", 0x1008, -1),
+    ("kv_start", None, -1), ("q_dtype", 7, -2), ("kv_dtype", 2, -2), ("flags", 0, -1),
+]
+
+
+@pytest.mark.parametrize("field,value,code", BROKEN)
+def test_fmha_entry_points_reject_bad_arguments_on_the_host(field, value, code):
+    """msa_fmha_fwd and msa_fmha_fwd_split_static share one argument check; both must answer
+    with an error code (never launch) for each broken argument."""
+    L = _lib()
+    for static in (False, True):
+        p = _valid_params(L)
+        if static:
+            p.num_splits = 2
+        setattr(p, field, value)
+        if static:
+            rc = L.lib.msa_fmha_fwd_split_static(ctypes.byref(p), None, None)
+        else:
+            rc = L.lib.msa_fmha_fwd(ctypes.byref(p), None)
+        assert rc == code, (field, value, static, rc)
+
+
+def test_sparse_and_paged_argument_rules():
+    L = _lib()
+    for static in (False, True):
+        call = (lambda p: L.lib.msa_fmha_fwd_split_static(ctypes.byref(p), None, None)) if static else \
+               (lambda p: L.lib.msa_fmha_fwd(ctypes.byref(p), None))
+        p = _valid_params(L)                      # paged without a page table
+        p.page_size = 128
+        assert call(p) == -1
+        p = _valid_params(L)                      # sparse on pages that are not 128 keys
+        p.flags = L.FLAG_OUT_O | L.FLAG_SPARSE
+        p.page_size, p.kv_page_indptr, p.kv_indices = 64, 0x1000, 0x1000
+        p.kv_block_indexes, p.token_batch, p.kv_block_num = 0x1000, 0x1000, 4
+        assert call(p) == -2
+        p.page_size, p.token_batch = 128, None     # sparse without the token -> batch map
+        assert call(p) == -1
+        p.token_batch, p.pack = 0x1000, 2          # sparse must fold the whole head group
+        assert call(p) == -1
+    p = _valid_params(L)                          # the static entry owns its scratch and has a size limit
+    p.num_splits, p.partial_o = 2, 0x1000
+    assert L.lib.msa_fmha_fwd_split_static(ctypes.byref(p), None, None) == -1
+    p = _valid_params(L)
+    p.num_splits, p.total_q, p.num_qo_heads, p.num_kv_heads, p.pack = 8, 64, 64, 64, 1
+    assert L.lib.msa_fmha_fwd_split_static(ctypes.byref(p), None, None) == -4
+
+
+def test_shipped_library_exports_no_debug_hooks():
+    """Tracing / test hooks exist only in builds with -DMSA_DEBUG_HOOKS."""
+    import subprocess
+    L = _lib()
+    out = subprocess.run(["nm", "-D", "--defined-only", L.LIB_PATH], capture_output=True, text=True).stdout
+    names = {ln.split()[-1] for ln in out.splitlines() if ln.strip()}
+    assert not [n for n in names if n.startswith("msa_debug")], names
+    assert set(L.EXPORTS) <= names

@@ -480,27 +480,28 @@ def test_proxy_scores_few_rows(fp8, hq, qo_lens):
 
 
 def test_sparse_page_major_global_index_kernels():
-    """The counting sort has two implementations: a shared-memory histogram per CTA (page table of up
-    to 12 288 pages) and one global atomic per selection (larger).  Force the second on a small case."""
+    """The counting sort has two implementations: a shared-memory histogram per CTA (page tables of up
+    to 12 288 logical pages) and one global atomic per selection (longer tables).  A 1.6 M-token
+    sequence whose 12 400 logical pages map onto a small physical pool takes the second."""
     api = _api()
-    from msa_for_sail import _lib, api as api_mod
+    from msa_for_sail import api as api_mod
     g = gen(4242)
-    qo_lens, kv_lens, hq, hk, kbn = [300, 77], [1500, 700], 8, 2, 8
+    n_logical, n_pool = 12400, 48
+    qo_lens, kv_lens, hq, hk, kbn = [300], [n_logical * 128 - 50], 8, 2, 8
     q = randn_bf16(g, sum(qo_lens), hq, 128)
-    kp, vp, table = make_paged(g, kv_lens, hk, 128)
-    offs = [kv_lens[i] - qo_lens[i] for i in range(len(qo_lens))]
+    kp = randn_bf16(g, n_pool, hk, 128, 128); vp = randn_bf16(g, n_pool, hk, 128, 128)
+    table = torch.randint(0, n_pool, (n_logical,), generator=g).to(torch.int32)
+    offs = [kv_lens[0] - qo_lens[0]]
     bi = random_blocks(g, qo_lens, kv_lens, offs, hk, kbn)
     ref = orc.sparse_attention(q, kp, vp, qo_lens, kv_lens, table, bi, hq)
     plan = api.fmha_sail_plan(_i32(qo_lens), _i32(kv_lens), hq, num_kv_heads=hk, page_size=128, kv_block_num=kbn)
     old = api_mod._FORCE_SPARSE_TC
     api_mod._FORCE_SPARSE_TC = True
-    _lib.lib.msa_debug_sparse_force_global_index(1)
     try:
         out, _ = api.fmha_sail(q.to(DEV), kp.to(DEV), vp.to(DEV), plan, kv_indices=table.to(DEV),
                                kv_block_indexes=bi.to(DEV))
         torch.cuda.synchronize()
     finally:
-        _lib.lib.msa_debug_sparse_force_global_index(0)
         api_mod._FORCE_SPARSE_TC = old
     check_out(out, ref, "sparse-global-index")
 

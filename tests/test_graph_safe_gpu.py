@@ -167,7 +167,8 @@ def test_plan_device_fills_what_its_header_says(causal, paged):
         assert np.array_equal(indptr.cpu().numpy(), np.concatenate([[0], np.cumsum((kl + 127) // 128)]))
     tb = token_batch.cpu().numpy()
     assert np.array_equal(tb[:ql.sum()], np.repeat(np.arange(batch), ql)) and (tb[ql.sum():] == 0).all()
-    assert (spr.cpu().numpy() == S).all()
+    sp = spr.cpu().numpy()
+    assert (sp[:ql.sum()] == S).all() and (sp[ql.sum():] == 0).all()     # padding rows: no splits to merge
     w = work.cpu().numpy().reshape(batch, groups, S, 8)
     for b in range(batch):
         nrows = min(block_m, int(ql[b]) * pack)
@@ -220,6 +221,8 @@ def test_chunked_prefill_plan_and_run_in_one_graph(splits):
         k = orc.paged_to_contiguous(kp, tables[i], kl, 128)
         v = orc.paged_to_contiguous(vp, tables[i], kl, 128)
         check_out(out[:n], orc.attention(q[:n], k, v, ql, kl, hq, hk), name)
+        if splits > 1:                                   # rows past the last token are merged from nothing
+            assert (out[n:] == 0).all(), f"{name}: padded rows are not zero"
 
     load(0)
     step()
@@ -230,7 +233,7 @@ def test_chunked_prefill_plan_and_run_in_one_graph(splits):
         step()
     for i in (1, 2, 0):
         load(i)
-        out.zero_()
+        out.fill_(3.0)                                   # every real row, and with splits the padding, is rewritten
         graph.replay()
         torch.cuda.synchronize()
         check(i, f"prefill graph-safe replay {i}")

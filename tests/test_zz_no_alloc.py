@@ -1,5 +1,5 @@
 """The allocation-free split-KV entry point (msa_fmha_fwd_split_static) against the regular
-split path (msa_fmha_fwd + msa_lse_merge with a caller-owned workspace).
+split path (msa_fmha_fwd + msa_lse_merge with a caller-owned workspace) and against the CPU oracle.
 
 The entry point is for embedders that must not allocate device memory when they call into the
 library (an engine whose own pool owns the device heap, a sandboxed plugin host): its per-split
@@ -12,7 +12,8 @@ import ctypes
 import pytest
 import torch
 
-from helpers import BF16_COS, BF16_MAX_ABS, gen, randn_bf16
+from helpers import BF16_COS, BF16_MAX_ABS, check_out, gen, randn_bf16
+from oracle import msa_oracle as orc
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -42,12 +43,13 @@ def _params_from_plan(L, plan, q, k, v, out, lse):
     return p
 
 
-def _one_round(api, L, seed, kv_lens, hq, hk, splits):
+def _one_round(api, L, seed, kv_lens, hq, hk, splits, pass_spr=True):
     g = gen(seed)
     n = len(kv_lens)
-    q = randn_bf16(g, n, hq, 128).to(DEV)
-    k = randn_bf16(g, sum(kv_lens), hk, 128).to(DEV)
-    v = randn_bf16(g, sum(kv_lens), hk, 128).to(DEV)
+    q_h = randn_bf16(g, n, hq, 128)
+    k_h = randn_bf16(g, sum(kv_lens), hk, 128)
+    v_h = randn_bf16(g, sum(kv_lens), hk, 128)
+    q, k, v = q_h.to(DEV), k_h.to(DEV), v_h.to(DEV)
     lens = torch.ones(n, dtype=torch.int32)
     plan = api.fmha_sail_plan(lens, torch.tensor(kv_lens, dtype=torch.int32), hq, num_kv_heads=hk,
                               num_kv_splits=splits)
@@ -60,9 +62,19 @@ def _one_round(api, L, seed, kv_lens, hq, hk, splits):
     lse = torch.full((n, hq), 7.0, dtype=torch.float32, device=DEV)
     p = _params_from_plan(L, pl, q, k, v, out, lse)
     spr = pl["num_kv_splits_per_row"]
-    rc = L.lib.msa_fmha_fwd_split_static(ctypes.byref(p), spr.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    free0, alloc0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    rc = L.lib.msa_fmha_fwd_split_static(ctypes.byref(p), spr.data_ptr() if pass_spr else None,
+                                         torch.cuda.current_stream().cuda_stream)
     assert rc == 0, L.lib.msa_status_string(rc)
     torch.cuda.synchronize()
+    # the call takes no device memory, neither from the driver nor from torch's pool
+    assert torch.cuda.memory_allocated() == alloc0
+    if getattr(_one_round, "warm", False):               # the first call on a device resolves the array's address
+        assert torch.cuda.mem_get_info()[0] >= free0
+    _one_round.warm = True
+    ones = [1] * n
+    check_out(out, orc.attention(q_h, k_h, v_h, ones, kv_lens, hq, hk), "static scratch vs oracle")
     a, b = out.float().cpu(), out_ref.float().cpu()
     assert torch.isfinite(a).all()
     assert (a - b).abs().max().item() <= BF16_MAX_ABS
@@ -76,6 +88,16 @@ def test_static_scratch_matches_regular_split_path_twice():
     from msa_for_sail import _lib as L
     _one_round(api, L, 1, [3000, 700, 2000, 129], 16, 2, 4)     # fills a large part of the scratch
     _one_round(api, L, 2, [1500, 260], 8, 2, 3)                 # smaller problem on the stale scratch
+
+
+def test_static_scratch_ignores_slots_no_work_item_wrote():
+    """Without splits_per_row the merge looks at all S slots of every token.  The 129-key sequence
+    has one key tile, hence one work item per head group: its other slots are written by nobody in
+    this call and still hold the partials of the larger call before it.  They must count as empty."""
+    import msa_for_sail as api
+    from msa_for_sail import _lib as L
+    _one_round(api, L, 3, [4000, 3000, 2500, 3500], 16, 2, 4)
+    _one_round(api, L, 4, [129, 1800, 140], 16, 2, 4, pass_spr=False)
 
 
 def test_static_scratch_rejects_oversize_and_foreign_workspace():
