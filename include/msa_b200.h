@@ -132,6 +132,21 @@ int msa_lse_merge(const void* partial_o, int32_t partial_dtype /* MSA_DT_F32 | M
                   int64_t out_stride_tok, int64_t out_stride_head,
                   float out_scale, msa_stream_t stream);
 
+/* The same merge with two more degrees of freedom, for partials that do not sit in the dense
+ * [S, total_q, H, ...] arrangement and for callers that want the result unrounded:
+ *  - o_split_stride / lse_split_stride: elements between split s and split s + 1 of partial_o /
+ *    partial_lse (<= 0: the dense default total_q*H*128 / total_q*H).  Lets one buffer hold
+ *    several ranks' packed (O, LSE) blocks as an all-gather delivers them;
+ *  - out_dtype: MSA_DT_BF16 or MSA_DT_F32 (the fp32 result of a local merge is what a rank
+ *    contributes to a cross-GPU merge).
+ * No upstream counterpart beyond `reduction` itself (upstream is single-device). */
+int msa_lse_merge_ex(const void* partial_o, int32_t partial_dtype, const float* partial_lse,
+                     const int32_t* splits_per_row, void* out, int32_t out_dtype, float* lse_out,
+                     int32_t num_splits, int32_t total_q, int32_t num_heads,
+                     int64_t o_split_stride, int64_t lse_split_stride,
+                     int64_t out_stride_tok, int64_t out_stride_head,
+                     float out_scale, msa_stream_t stream);
+
 /* Page top-k: per (head, token) row of scores[H, K, T] pick the `topk` best
  * pages of [0, num_valid_pages) by (score desc, index asc), emit them
  * ascending into out[T, H, topk] (int32), pad with -1.  Pages [0, force_begin)

@@ -13,11 +13,12 @@ namespace {
 
 // Half a warp per (token, head) row: lane l of the half owns columns 8l..8l+7.  Loads of up to
 // eight splits are issued back to back before they are consumed.
-template <bool PBF16>
+template <bool PBF16, bool OF32>
 __global__ void __launch_bounds__(256)
 lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, const int32_t* __restrict__ spr,
-                 __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int num_splits, int total_q,
-                 int num_heads, int64_t out_stride_tok, int64_t out_stride_head, float out_scale) {
+                 void* __restrict__ out_, float* __restrict__ lse_out, int num_splits, int total_q,
+                 int num_heads, int64_t o_split_stride, int64_t l_split_stride, int64_t out_stride_tok,
+                 int64_t out_stride_head, float out_scale) {
   const int l16 = threadIdx.x & 15;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4);   // t * H + h
   const int64_t rows = static_cast<int64_t>(total_q) * num_heads;
@@ -26,7 +27,7 @@ lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, con
   const int S = spr ? min(spr[t], num_splits) : num_splits;
 
   float mx = -INFINITY;
-  for (int s = 0; s < S; ++s) mx = fmaxf(mx, __ldg(pl + static_cast<int64_t>(s) * rows + row));
+  for (int s = 0; s < S; ++s) mx = fmaxf(mx, __ldg(pl + static_cast<int64_t>(s) * l_split_stride + row));
   const float mxs = (mx == -INFINITY) ? 0.f : mx;
 
   float acc[8];
@@ -40,14 +41,14 @@ lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, con
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int s = min(s0 + u, S - 1);                         // clamped: always a readable slot
-      const int64_t base = (static_cast<int64_t>(s) * rows + row) * kHeadDim + l16 * 8;
+      const int64_t base = static_cast<int64_t>(s) * o_split_stride + row * kHeadDim + l16 * 8;
       if constexpr (PBF16) {
         raw[u][0] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(po_) + base);
       } else {
         raw[u][0] = *reinterpret_cast<const uint4*>(static_cast<const float*>(po_) + base);
         raw[u][1] = *reinterpret_cast<const uint4*>(static_cast<const float*>(po_) + base + 4);
       }
-      const float l = __ldg(pl + static_cast<int64_t>(s) * rows + row);
+      const float l = __ldg(pl + static_cast<int64_t>(s) * l_split_stride + row);
       w[u] = (s0 + u < S && l != -INFINITY) ? __expf(l - mxs) : 0.f;
     }
 #pragma unroll
@@ -70,8 +71,12 @@ lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, con
     }
   }
   const float inv = sw > 0.f ? out_scale / sw : 0.f;
-  if (out) {
-    __nv_bfloat16* dst = out + static_cast<int64_t>(t) * out_stride_tok + static_cast<int64_t>(h) * out_stride_head + l16 * 8;
+  if (out_ && OF32) {
+    float* dst = static_cast<float*>(out_) + static_cast<int64_t>(t) * out_stride_tok + static_cast<int64_t>(h) * out_stride_head + l16 * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+  } else if (out_) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out_) + static_cast<int64_t>(t) * out_stride_tok + static_cast<int64_t>(h) * out_stride_head + l16 * 8;
     uint4 pk;
     pk.x = pack2<false>(acc[0] * inv, acc[1] * inv);
     pk.y = pack2<false>(acc[2] * inv, acc[3] * inv);
@@ -85,10 +90,11 @@ lse_merge_kernel(const void* __restrict__ po_, const float* __restrict__ pl, con
 }  // namespace
 }  // namespace msa
 
-extern "C" int msa_lse_merge(const void* partial_o, int32_t partial_dtype, const float* partial_lse,
-                             const int32_t* splits_per_row, void* out, float* lse_out, int32_t num_splits,
-                             int32_t total_q, int32_t num_heads, int64_t out_stride_tok, int64_t out_stride_head,
-                             float out_scale, msa_stream_t stream) {
+extern "C" int msa_lse_merge_ex(const void* partial_o, int32_t partial_dtype, const float* partial_lse,
+                                const int32_t* splits_per_row, void* out, int32_t out_dtype, float* lse_out,
+                                int32_t num_splits, int32_t total_q, int32_t num_heads, int64_t o_split_stride,
+                                int64_t lse_split_stride, int64_t out_stride_tok, int64_t out_stride_head,
+                                float out_scale, msa_stream_t stream) {
   if (!partial_o || !partial_lse || (!out && !lse_out) || num_splits < 1 || total_q < 0 || num_heads <= 0)
     return MSA_ERR_BAD_ARG;
   const int64_t rows = static_cast<int64_t>(total_q) * num_heads;
@@ -96,13 +102,31 @@ extern "C" int msa_lse_merge(const void* partial_o, int32_t partial_dtype, const
   const int64_t blocks = (rows + 15) / 16;
   if (blocks > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   if (partial_dtype != MSA_DT_F32 && partial_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
-  if (partial_dtype == MSA_DT_BF16)
-    msa::lse_merge_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        partial_o, partial_lse, splits_per_row, static_cast<__nv_bfloat16*>(out), lse_out, num_splits, total_q,
-        num_heads, out_stride_tok, out_stride_head, out_scale);
-  else
-    msa::lse_merge_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        partial_o, partial_lse, splits_per_row, static_cast<__nv_bfloat16*>(out), lse_out, num_splits, total_q,
-        num_heads, out_stride_tok, out_stride_head, out_scale);
+  if (out_dtype != MSA_DT_F32 && out_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
+  if (o_split_stride <= 0) o_split_stride = rows * msa::kHeadDim;
+  if (lse_split_stride <= 0) lse_split_stride = rows;
+  // rows are read and written 16 bytes at a time
+  const int pe = partial_dtype == MSA_DT_BF16 ? 2 : 4, oe = out_dtype == MSA_DT_BF16 ? 2 : 4;
+  auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+  if (!al(partial_o) || (o_split_stride * pe) % 16 || (out && (!al(out) || (out_stride_tok * oe) % 16 ||
+                                                                (out_stride_head * oe) % 16)))
+    return MSA_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned nb = static_cast<unsigned>(blocks);
+#define MSA_MERGE_CASE(PB, OF)                                                                                       \
+  msa::lse_merge_kernel<PB, OF><<<nb, 256, 0, st>>>(partial_o, partial_lse, splits_per_row, out, lse_out, num_splits, \
+                                                    total_q, num_heads, o_split_stride, lse_split_stride,           \
+                                                    out_stride_tok, out_stride_head, out_scale)
+  if (partial_dtype == MSA_DT_BF16) { if (out_dtype == MSA_DT_F32) MSA_MERGE_CASE(true, true); else MSA_MERGE_CASE(true, false); }
+  else { if (out_dtype == MSA_DT_F32) MSA_MERGE_CASE(false, true); else MSA_MERGE_CASE(false, false); }
+#undef MSA_MERGE_CASE
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
+}
+
+extern "C" int msa_lse_merge(const void* partial_o, int32_t partial_dtype, const float* partial_lse,
+                             const int32_t* splits_per_row, void* out, float* lse_out, int32_t num_splits,
+                             int32_t total_q, int32_t num_heads, int64_t out_stride_tok, int64_t out_stride_head,
+                             float out_scale, msa_stream_t stream) {
+  return msa_lse_merge_ex(partial_o, partial_dtype, partial_lse, splits_per_row, out, MSA_DT_BF16, lse_out, num_splits,
+                          total_q, num_heads, 0, 0, out_stride_tok, out_stride_head, out_scale, stream);
 }

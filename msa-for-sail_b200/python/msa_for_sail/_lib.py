@@ -62,7 +62,7 @@ class MsaPlanDeviceArgs(ctypes.Structure):
 #: every symbol include/msa_b200.h declares
 EXPORTS = ("msa_fmha_fwd", "msa_lse_merge", "msa_topk_select", "msa_plan_dense",
            "msa_status_string", "msa_build_arch", "msa_sizeof", "msa_fmha_fwd_split_static",
-           "msa_sparse_workspace_bytes", "msa_plan_device")
+           "msa_sparse_workspace_bytes", "msa_plan_device", "msa_lse_merge_ex")
 
 
 def _load():
@@ -85,6 +85,8 @@ def _load():
     lib.msa_fmha_fwd.restype = ctypes.c_int
     lib.msa_lse_merge.argtypes = [_p, _i32, _p, _p, _p, _p, _i32, _i32, _i32, _i64, _i64, _f32, _p]
     lib.msa_lse_merge.restype = ctypes.c_int
+    lib.msa_lse_merge_ex.argtypes = [_p, _i32, _p, _p, _p, _i32, _p, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _f32, _p]
+    lib.msa_lse_merge_ex.restype = ctypes.c_int
     lib.msa_topk_select.argtypes = [_p, _i32, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _p]
     lib.msa_topk_select.restype = ctypes.c_int
     lib.msa_plan_dense.argtypes = [ctypes.POINTER(MsaPlanArgs), _p, _i32, _p, _p]

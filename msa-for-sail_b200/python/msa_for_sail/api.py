@@ -657,7 +657,9 @@ def _fmha_sail(
     Extension over upstream: ``lse`` -- a preallocated fp32 ``[total_q, Hq]``
     buffer that receives the natural-log LSE of every row; ``k_scale`` /
     ``v_scale`` may be fp32 tensors with one entry per KV head; bf16 ``q`` may
-    be combined with e4m3 ``k``/``v``."""
+    be combined with e4m3 ``k``/``v``; a preallocated ``out`` may be fp32 (the
+    unrounded result, what a rank hands to a cross-GPU merge: written by the
+    split-KV merge directly, converted from the bf16 result otherwise)."""
     if not q.is_cuda:
         raise RuntimeError("fmha_sail needs CUDA tensors (there is no CPU path)")
     nnz_qo, num_qo_heads, head_dim_qk = q.shape
@@ -750,7 +752,7 @@ def _fmha_sail(
     elif out is None:
         out = torch.empty(nnz_qo, num_qo_heads, head_dim_vo, device=q.device, dtype=torch.bfloat16)
     else:
-        assert out.dtype == torch.bfloat16 and out.shape == (nnz_qo, num_qo_heads, head_dim_vo)
+        assert out.dtype in (torch.bfloat16, torch.float32) and out.shape == (nnz_qo, num_qo_heads, head_dim_vo)
         assert out.stride(2) == 1
 
     if nnz_qo == 0:
@@ -788,9 +790,7 @@ def _fmha_sail(
               and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
               and page_size in (0, 128) and _USE_TC and (plan["tc_preferred"] or _FORCE_TC))
     use_split = output_o and splits > 1 and not use_tc
-    if out is not None:
-        p.out = out.data_ptr()
-        p.out_stride_tok, p.out_stride_head = out.stride(0), out.stride(1)
+    kernel_out = out                             # what the attention kernel itself writes (bf16)
     if lse is not None:
         assert lse.dtype == torch.float32 and lse.is_contiguous() and lse.shape == (nnz_qo, num_qo_heads)
     if use_split:
@@ -837,6 +837,12 @@ def _fmha_sail(
     else:
         p.work = _ptr(plan["work"])
         p.num_work = plan["num_work"]
+    if out is not None and out.dtype == torch.float32:
+        # the split path's merge writes fp32 itself; an unsplit kernel writes bf16, converted below
+        kernel_out = None if use_split else torch.empty(out.shape, dtype=torch.bfloat16, device=out.device)
+    if kernel_out is not None:
+        p.out = kernel_out.data_ptr()
+        p.out_stride_tok, p.out_stride_head = kernel_out.stride(0), kernel_out.stride(1)
     p.k_scale_head, p.v_scale_head = _ptr(k_head), _ptr(v_head)
     p.total_q, p.num_qo_heads, p.num_kv_heads, p.batch = nnz_qo, num_qo_heads, num_kv_heads, batch
     p.block_m, p.pack = plan["qo_tile_size"], plan["pack_factor"]
@@ -863,11 +869,21 @@ def _fmha_sail(
 
     if use_split:
         spr = plan["num_kv_splits_per_row"]
-        _lib.check(_lib.lib.msa_lse_merge(
+        _lib.check(_lib.lib.msa_lse_merge_ex(
             plan["workspace_o"].data_ptr(), MSA_DT_F32, plan["workspace_lse"].data_ptr(), _ptr(spr),
-            out.data_ptr(), _ptr(lse), splits, nnz_qo, num_qo_heads,
-            out.stride(0), out.stride(1), float(v_s * o_s), stream), "msa_lse_merge")
+            out.data_ptr(), _dt_code(out.dtype), _ptr(lse), splits, nnz_qo, num_qo_heads, 0, 0,
+            out.stride(0), out.stride(1), float(v_s * o_s), stream), "msa_lse_merge_ex")
+    elif kernel_out is not None and kernel_out is not out:
+        out.copy_(kernel_out)
     return out, max_score
+
+
+def _decode_prefix(qo_segment_lens, sparse):
+    """Length of the leading run of short-query (decode) batch items when the batch also holds a
+    long-query (prefill) item, else 0.  Items are expected decode-first, as upstream's mixed
+    batches are (api.py:1555-1575)."""
+    long_items = (qo_segment_lens > _prefill_qlen_threshold(sparse)).nonzero(as_tuple=False)
+    return int(long_items[0, 0].item()) if long_items.numel() else 0
 
 
 def fmha_sail_plan(
@@ -885,37 +901,71 @@ def fmha_sail_plan(
     (forwarded to ``_fmha_sail_plan``): ``num_kv_heads``, ``num_kv_splits``,
     ``page_size``, ``output_maxscore``, ``kv_block_num``, ``usable_SM_count``,
     ``causal``, ``use_fp8_kvcache``, ``device``, ``stream``, ``given_workspace``,
-    ``max_total_q``, ``graph_safe`` and the ``*_override`` hints.
+    ``max_total_q``, ``graph_safe`` and the ``*_override`` hints.  With
+    ``split_prefill_decode`` a decode-first batch is planned as two sub-batches, each with
+    the tile shape that suits it.
     """
-    if qo_offset is not None and isinstance(qo_offset, int):
-        if kwargs.get("graph_safe", False):
+    graph_safe = bool(kwargs.get("graph_safe", False))
+    if isinstance(qo_offset, int):
+        if graph_safe:
             raise ValueError(
                 "graph_safe=True requires qo_offset as a CUDA tensor; an int "
                 "triggers an in-capture torch.full_like allocation")
         qo_offset = torch.full_like(qo_segment_lens, qo_offset)
+    batch_size = int(qo_segment_lens.shape[0])
+    cut = 0
+    if split_prefill_decode and not graph_safe and batch_size:
+        cut = _decode_prefix(qo_segment_lens, kwargs.get("kv_block_num", -1) > 0)
+    pieces = [slice(0, batch_size)] if cut == 0 else [slice(0, cut), slice(cut, batch_size)]
+    plans = [_fmha_sail_plan(qo_segment_lens[s], kv_segment_lens[s], *args,
+                             qo_offset=None if qo_offset is None else qo_offset[s], **kwargs) for s in pieces]
+    return (cut > 0, cut, batch_size, plans[0], plans[1] if cut else None)
 
-    batch_size = qo_segment_lens.shape[0]
-    has_mixed_prefill = False
-    split = 0
-    if split_prefill_decode and kwargs.get("graph_safe", False):
-        split_prefill_decode = False
-    if split_prefill_decode:
-        qmax = qo_segment_lens.max().item()
-        sparse = kwargs.get("kv_block_num", -1) > 0
-        split_threshold = _prefill_qlen_threshold(sparse)
-        if qmax > split_threshold:
-            split = (qo_segment_lens > split_threshold).nonzero(as_tuple=False)[0, 0].item()
-            has_mixed_prefill = split > 0
-    if has_mixed_prefill:
-        d_off = qo_offset[:split] if qo_offset is not None else None
-        decode = _fmha_sail_plan(qo_segment_lens[:split], kv_segment_lens[:split], *args,
-                                 qo_offset=d_off, **kwargs)
-        p_off = qo_offset[split:] if qo_offset is not None else None
-        prefill = _fmha_sail_plan(qo_segment_lens[split:], kv_segment_lens[split:], *args,
-                                  qo_offset=p_off, **kwargs)
-        return (True, split, batch_size, decode, prefill)
-    plan = _fmha_sail_plan(qo_segment_lens, kv_segment_lens, *args, qo_offset=qo_offset, **kwargs)
-    return (False, 0, batch_size, plan, None)
+
+def _run_sub_batches(parts, q, k, v, kv_indices, kv_block_indexes, q_offset_override, out, max_score, kwargs):
+    """Run consecutive sub-batches, each with its own plan, over slices of one call's tensors.
+
+    ``parts``: ``[(plan, first batch item, one past the last)]`` in batch order.  Query tokens,
+    page-table entries (paged) or keys (ragged) of the sub-batches follow one another in the
+    inputs, so every sub-call sees plain slices; O and the LSE are written straight into slices of
+    the combined buffers, per-tile scores are copied into a combined ``max_score`` (the
+    sub-batches' tile counts differ)."""
+    nnz_qo, num_qo_heads = q.shape[0], q.shape[1]
+    paged = kv_indices is not None
+    lse = kwargs.pop("lse", None)
+    want_o = kwargs.get("output_o", True)
+    if want_o and out is None:
+        out = torch.empty(nnz_qo, num_qo_heads, v.shape[-1], device=q.device, dtype=torch.bfloat16)
+    tok = kv = 0
+    scores = []
+    for plan, b0, b1 in parts:
+        n_tok = plan["total_qo_len"]
+        kv_lens = plan["_host"]["kv_lens"]
+        ps = plan["page_size"]
+        n_kv = sum(-(-kl // ps) for kl in kv_lens) if paged else sum(kv_lens)
+        rows, span = slice(tok, tok + n_tok), slice(kv, kv + n_kv)
+        off = q_offset_override[b0:b1] if isinstance(q_offset_override, torch.Tensor) else q_offset_override
+        _, ms = _fmha_sail(
+            q[rows], k if paged else k[span], v if paged else v[span], plan,
+            kv_indices=kv_indices[span] if paged else None,
+            kv_block_indexes=None if kv_block_indexes is None else kv_block_indexes[rows],
+            q_offset_override=off, out=out[rows] if want_o else None, max_score=None,
+            lse=None if lse is None else lse[rows], **kwargs)
+        scores.append((rows, ms))
+        tok += n_tok
+        kv += n_kv
+    if all(ms is None for _, ms in scores):
+        return (out if want_o else None), None
+    tiles = max(ms.shape[1] for _, ms in scores if ms is not None)
+    dtype = next(ms.dtype for _, ms in scores if ms is not None)
+    if max_score is None:
+        max_score = torch.full((num_qo_heads, tiles, nnz_qo), -float("inf"), dtype=dtype, device=q.device)
+    else:
+        max_score.fill_(-float("inf"))
+    for rows, ms in scores:
+        if ms is not None:
+            max_score[:, :ms.shape[1], rows] = ms
+    return (out if want_o else None), max_score
 
 
 def fmha_sail(
@@ -940,66 +990,13 @@ def fmha_sail(
     ``max_score_dtype``, ``check_input_valid``.  Returns ``(out, max_score)``; either may be
     ``None`` when that output is disabled.
     """
-    has_mixed_prefill, split, batch_size, decode, prefill = plan_info
-    if not has_mixed_prefill:
-        return _fmha_sail(q, k, v, decode, out=out, max_score=max_score, kv_indices=kv_indices,
+    mixed, cut, batch_size, first, second = plan_info
+    if not mixed:
+        return _fmha_sail(q, k, v, first, out=out, max_score=max_score, kv_indices=kv_indices,
                           kv_block_indexes=kv_block_indexes, q_offset_override=q_offset_override,
                           **kwargs)
-
-    decode_nnz = decode["total_qo_len"]
-    is_paged = kv_indices is not None
-    nnz_qo, num_qo_heads = q.shape[0], q.shape[1]
-    q_decode, q_prefill = q[:decode_nnz], q[decode_nnz:]
-    if is_paged:
-        k_decode = k_prefill = k
-        v_decode = v_prefill = v
-        kv_page_split = int(decode["kv_page_indptr"][-1].item())
-        decode_kv_indices = kv_indices[:kv_page_split]
-        prefill_kv_indices = kv_indices[kv_page_split:]
-    else:
-        decode_kv_nnz = sum(decode["_host"]["kv_lens"])
-        k_decode, k_prefill = k[:decode_kv_nnz], k[decode_kv_nnz:]
-        v_decode, v_prefill = v[:decode_kv_nnz], v[decode_kv_nnz:]
-        decode_kv_indices = prefill_kv_indices = None
-    decode_block_idx = kv_block_indexes[:decode_nnz] if kv_block_indexes is not None else None
-    prefill_block_idx = kv_block_indexes[decode_nnz:] if kv_block_indexes is not None else None
-    if isinstance(q_offset_override, int):
-        decode_qo_offset = torch.full((split,), q_offset_override, dtype=torch.int32, device=q.device)
-        prefill_qo_offset = torch.full((batch_size - split,), q_offset_override, dtype=torch.int32,
-                                       device=q.device)
-    elif q_offset_override is not None:
-        decode_qo_offset, prefill_qo_offset = q_offset_override[:split], q_offset_override[split:]
-    else:
-        decode_qo_offset = prefill_qo_offset = None
-
-    lse = kwargs.pop("lse", None)
-    decode_out, decode_ms = _fmha_sail(
-        q_decode, k_decode, v_decode, decode, out=None, max_score=None,
-        kv_indices=decode_kv_indices, kv_block_indexes=decode_block_idx,
-        q_offset_override=decode_qo_offset, lse=None if lse is None else lse[:decode_nnz], **kwargs)
-    prefill_out, prefill_ms = _fmha_sail(
-        q_prefill, k_prefill, v_prefill, prefill, out=None, max_score=None,
-        kv_indices=prefill_kv_indices, kv_block_indexes=prefill_block_idx,
-        q_offset_override=prefill_qo_offset, lse=None if lse is None else lse[decode_nnz:], **kwargs)
-
-    if decode_out is not None and prefill_out is not None:
-        combined_out = torch.cat([decode_out, prefill_out], dim=0)
-    else:
-        combined_out = None
-    if out is not None and combined_out is not None:
-        out.copy_(combined_out)
-    if decode_ms is not None and prefill_ms is not None:
-        d_kt, p_kt = decode_ms.shape[1], prefill_ms.shape[1]
-        combined_ms = torch.full((num_qo_heads, max(d_kt, p_kt), nnz_qo), -float("inf"),
-                                 dtype=decode_ms.dtype, device=q.device)
-        combined_ms[:, :d_kt, :decode_nnz] = decode_ms
-        combined_ms[:, :p_kt, decode_nnz:] = prefill_ms
-    else:
-        combined_ms = decode_ms if decode_ms is not None else prefill_ms
-    if max_score is not None and combined_ms is not None:
-        max_score.copy_(combined_ms)
-    return (out if out is not None else combined_out,
-            max_score if max_score is not None else combined_ms)
+    return _run_sub_batches([(first, 0, cut), (second, cut, batch_size)], q, k, v, kv_indices, kv_block_indexes,
+                            q_offset_override, out, max_score, dict(kwargs))
 
 
 # ============================================================================
@@ -1021,39 +1018,30 @@ def sparse_topk_select(
     the tail when fewer than ``topk`` pages exist.  Ranking is (score desc, index asc), so the
     result is deterministic for both dtypes.  ``topk`` may be 4, 8, 16 (upstream: 16 only) or 32.
     """
-    assert max_score.dtype == torch.float32 or max_score.dtype == torch.bfloat16, \
+    if not isinstance(max_score, torch.Tensor) or max_score.dim() != 3:
+        raise AssertionError(f"max_score must be 3D, got {getattr(max_score, 'shape', None)}")
+    assert max_score.dtype in (torch.float32, torch.bfloat16), \
         f"max_score must be float32 or bfloat16, got {max_score.dtype}"
-    assert max_score.dim() == 3, f"max_score must be 3D, got {max_score.shape}"
     assert max_score.is_contiguous(), "max_score must be contiguous"
     assert topk in (4, 8, 16, 32), f"topk must be 4, 8, 16 or 32, got {topk}"
     if not max_score.is_cuda:
         raise RuntimeError("sparse_topk_select needs a CUDA tensor (there is no CPU path)")
-
     num_qo_heads, max_k_tiles, total_qo_len = max_score.shape
-    if num_valid_pages is not None:
-        assert 0 < num_valid_pages <= max_k_tiles, (
-            f"num_valid_pages={num_valid_pages} must be in (0, max_k_tiles={max_k_tiles}]")
-        nvp_arg = int(num_valid_pages)
+    nvp = max_k_tiles if num_valid_pages is None else int(num_valid_pages)
+    assert 0 < nvp <= max_k_tiles, f"num_valid_pages={nvp} must be in (0, max_k_tiles={max_k_tiles}]"
+    fb, fe = int(force_begin_blocks), int(force_end_blocks)
+    assert fb >= 0 and fe >= 0, (
+        f"force_begin_blocks={fb} and force_end_blocks={fe} must be non-negative")
+    assert fb + fe <= topk, (
+        f"force_begin_blocks({fb}) + force_end_blocks({fe}) = {fb + fe} exceeds topk={topk}")
+    shape = (total_qo_len, num_qo_heads, topk)
+    if output is None:
+        output = torch.empty(shape, dtype=torch.int32, device=max_score.device)
     else:
-        nvp_arg = int(max_k_tiles)
-    assert force_begin_blocks >= 0 and force_end_blocks >= 0, (
-        f"force_begin_blocks={force_begin_blocks} and force_end_blocks={force_end_blocks} "
-        f"must be non-negative")
-    assert force_begin_blocks + force_end_blocks <= topk, (
-        f"force_begin_blocks({force_begin_blocks}) + force_end_blocks({force_end_blocks}) "
-        f"= {force_begin_blocks + force_end_blocks} exceeds topk={topk}")
-
-    if output is not None:
-        output_indices = output
-        assert output.dtype == torch.int32 and output.is_contiguous()
-        assert tuple(output.shape) == (total_qo_len, num_qo_heads, topk)
-    else:
-        output_indices = torch.empty(total_qo_len, num_qo_heads, topk, dtype=torch.int32,
-                                     device=max_score.device)
+        assert output.dtype == torch.int32 and output.is_contiguous() and tuple(output.shape) == shape
     if total_qo_len == 0 or num_qo_heads == 0:
-        return output_indices
+        return output
     _lib.check(_lib.lib.msa_topk_select(
-        max_score.data_ptr(), _dt_code(max_score.dtype), output_indices.data_ptr(),
-        num_qo_heads, max_k_tiles, total_qo_len, topk, nvp_arg,
-        int(force_begin_blocks), int(force_end_blocks), _stream()), "msa_topk_select")
-    return output_indices
+        max_score.data_ptr(), _dt_code(max_score.dtype), output.data_ptr(),
+        num_qo_heads, max_k_tiles, total_qo_len, topk, nvp, fb, fe, _stream()), "msa_topk_select")
+    return output

@@ -1,5 +1,5 @@
 """World-size-2 check (gloo, CPU) of the context-parallel decode exchange: each rank attends to
-its own page range, the ranks all-gather (O, LSE) and merge.  The GPU code path does the same with
+its own page range, the ranks all-gather their packed (O, LSE) blocks and merge.  The GPU code path does the same with
 NCCL and the merge kernel; here the oracle stands in for both kernels so that the host-side logic
 (page-range sharding, gather layout, merge semantics incl. a rank that owns no key) is covered
 without a GPU."""
@@ -33,10 +33,13 @@ def _worker(rank, world, port, kv_len, ret):
         o, lse = orc.attention(q, k[s:e], v[s:e], [1], [e - s], hq, hk, causal=False, return_lse=True)
     else:                                            # this rank owns no key
         o, lse = torch.zeros(1, hq, 128), torch.full((1, hq), -float("inf"))
-    po_l, pl_l = mdist.pack_partials(o, lse)
-    po = torch.empty(world, 1, hq, 128); pl = torch.empty(world, 1, hq)
-    dist.all_gather_into_tensor(po.view(-1), po_l.view(-1))
-    dist.all_gather_into_tensor(pl.view(-1), pl_l.view(-1))
+    # the packed block of the exchange: [O: T*H*128 floats | LSE: T*H floats], one collective
+    ex = mdist.DecodeExchange(1, hq, torch.device("cpu"))
+    ex.o_local.copy_(o); ex.lse_local.copy_(lse)
+    dist.all_gather_into_tensor(ex.gathered, ex.local)
+    blocks = ex.gathered.view(world, ex.block)          # what the merge kernel is pointed at: split stride = block
+    po = blocks[:, :hq * 128].reshape(world, 1, hq, 128)
+    pl = blocks[:, hq * 128:].reshape(world, 1, hq)
     merged = orc.lse_merge(po, pl)
     full = orc.attention(q, k, v, [1], [kv_len], hq, hk, causal=False)
     ok = torch.allclose(merged, full, atol=1e-5, rtol=1e-5)
@@ -75,3 +78,6 @@ def test_shard_helpers():
         assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
         assert max(e - s for s, e in ranges) - min(e - s for s, e in ranges) <= 1
     assert sorted(sum((mdist.shard_units(32, r, 8) for r in range(8)), [])) == list(range(32))
+    for n, w in ((32, 8), (16, 4), (256, 8), (16, 2), (5, 2)):
+        blocks = [mdist.shard_units(n, r, w, contiguous=True) for r in range(w)]
+        assert sum(blocks, []) == list(range(n))            # contiguous, in rank order, nothing lost

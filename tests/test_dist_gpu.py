@@ -1,6 +1,7 @@
-"""Two-GPU check of the context-parallel decode: each rank runs `fmha_sail` over its own page
-range, NCCL all-gathers (O, LSE), the merge kernel combines them; compared with the oracle over
-the whole sequence.  Skipped on boxes with fewer than two GPUs."""
+"""Multi-GPU check of the context-parallel decode: each rank runs `fmha_sail` over its own page
+range, writing its unrounded fp32 (O, LSE) into the packed exchange block; one NCCL all-gather and the
+merge kernel combine them; compared with the oracle over the whole sequence.  Runs with 2, 4 and 8
+ranks where the box has that many GPUs (skipped otherwise)."""
 import os
 import sys
 
@@ -25,37 +26,44 @@ def _worker(rank, world, port, ret):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     g = torch.Generator().manual_seed(9)
-    hq, hk, page, n_pages = 16, 2, 128, 37
+    hq, hk, page, n_pages = 16, 2, 128, 37 * world
     kv_len = n_pages * page
     q = torch.randn(1, hq, 128, generator=g).to(torch.bfloat16)
     kp = torch.randn(n_pages, hk, page, 128, generator=g).to(torch.bfloat16)
     vp = torch.randn(n_pages, hk, page, 128, generator=g).to(torch.bfloat16)
     p0, p1 = mdist.shard_page_range(n_pages, rank, world)
     table = torch.arange(p1 - p0, dtype=torch.int32, device=dev)
-    plan = msa.fmha_sail_plan(torch.tensor([1], dtype=torch.int32), torch.tensor([(p1 - p0) * page], dtype=torch.int32),
-                              hq, num_kv_heads=hk, page_size=page, causal=False)
-    lse = torch.empty(1, hq, dtype=torch.float32, device=dev)
-    out, _ = msa.fmha_sail(q.to(dev), kp[p0:p1].to(dev), vp[p0:p1].to(dev), plan, kv_indices=table, lse=lse)
-    merged = mdist.decode_allgather_merge(out, lse)
-    torch.cuda.synchronize()
-    k = kp.permute(0, 2, 1, 3).reshape(kv_len, hk, 128); v = vp.permute(0, 2, 1, 3).reshape(kv_len, hk, 128)
-    ref = orc.attention(q, k, v, [1], [kv_len], hq, hk, causal=False)
-    err = (merged.float().cpu() - ref).abs().max().item()
+    lens = (torch.tensor([1], dtype=torch.int32), torch.tensor([(p1 - p0) * page], dtype=torch.int32))
+    errs = []
+    for splits in (-1, 1):              # split-KV (the merge writes fp32 itself) and unsplit (converted from bf16)
+        plan = msa.fmha_sail_plan(*lens, hq, num_kv_heads=hk, page_size=page, causal=False, num_kv_splits=splits)
+        ex = mdist.DecodeExchange(1, hq, dev)
+        msa.fmha_sail(q.to(dev), kp[p0:p1].to(dev), vp[p0:p1].to(dev), plan, kv_indices=table, **ex.local_kwargs())
+        merged = ex.allgather_merge()
+        torch.cuda.synchronize()
+        k = kp.permute(0, 2, 1, 3).reshape(kv_len, hk, 128); v = vp.permute(0, 2, 1, 3).reshape(kv_len, hk, 128)
+        ref = orc.attention(q, k, v, [1], [kv_len], hq, hk, causal=False)
+        errs.append((merged.float().cpu() - ref).abs().max().item())
+        # the convenience form on results that already exist
+        merged2 = mdist.decode_allgather_merge(ex.o_local.clone(), ex.lse_local.clone())
+        errs.append((merged2.float() - merged.float()).abs().max().item())
     dist.barrier()
     dist.destroy_process_group()
-    ret.put((rank, err))
+    ret.put((rank, max(errs)))
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_context_parallel_decode_nccl():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_context_parallel_decode_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, 29741, ret)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, 29741 + world, ret)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    errs = dict(ret.get(timeout=10) for _ in range(2))
+    errs = dict(ret.get(timeout=10) for _ in range(world))
     assert max(errs.values()) <= 2e-2, errs
