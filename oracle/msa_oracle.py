@@ -252,12 +252,16 @@ def sparse_attention(q, k_pages, v_pages, qo_lens, kv_lens, kv_indices, kv_block
 # ---------------------------------------------------------------------------
 
 def _ord_key(x: torch.Tensor) -> torch.Tensor:
-    """Order-preserving integer key of an fp32 score (NaN with sign bit clear
-    ranks above +inf), as int64.  Mirrors the upstream ``float_to_ord``
-    (``sparse_topk_select.cuh:186-196``)."""
-    bits = x.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    """Integer key of an fp32 score, as int64, whose order is the order a stable descending
+    ``torch.sort`` gives the scores: the upstream ``float_to_ord`` map
+    (``sparse_topk_select.cuh:186-196``) with the two cases in which bit order and value order
+    differ folded in -- -0.0 and +0.0 compare equal (one key), every NaN ranks above +inf and all
+    NaNs tie (one key)."""
+    x = x.contiguous() + 0.0                                  # -0.0 + 0.0 = +0.0
+    bits = x.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
     neg = (bits >> 31) & 1
-    return torch.where(neg == 1, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+    key = torch.where(neg == 1, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+    return torch.where(torch.isnan(x), torch.full_like(key, 0xFFFFFFFF), key)
 
 
 def topk_select(max_score, topk, num_valid_pages=None, force_begin_blocks=0,

@@ -13,7 +13,8 @@ reference code, imported unmodified and executed on CPU tensors:
 * ``tests/regression/test_sparse_attn.py``           ``sparse_ref``
 * the top-k contract of ``tests/smoke/test_sparse_topk_forced.py:266-275``
   (stable descending sort, first k, re-sorted ascending) evaluated with the
-  same torch calls on that file's seven score distributions (shrunk to K=512).
+  same torch calls on that file's seven score distributions (shrunk to K=512), plus two more
+  that the contract implies but the file does not exercise: zeros of both signs, and NaN.
 
 bf16 tensors are stored as their uint16 bit patterns.
 """
@@ -137,10 +138,21 @@ def main():
             m[:, 1::2, :] = 1.0078125
             m.scatter_(1, order[:, :7, :], 2.0)
             return m
+        # two distributions beyond the upstream file's seven, evaluated with the same stable-sort calls:
+        if kind == "signed-zero-sea":                # -0.0 and +0.0 compare equal: they tie, the lower index wins
+            sign = torch.rand(H, K, T, generator=gg) < 0.5
+            m = torch.where(sign, torch.tensor(-0.0), torch.tensor(0.0))
+            m.scatter_(1, order[:, :7, :], 2.0)
+            m.scatter_(1, order[:, 7:40, :], -1.0)
+            return m
+        if kind == "nan-sprinkled":                  # torch orders NaN above every number, NaNs tie among themselves
+            m = torch.randn(H, K, T, generator=gg)
+            m.scatter_(1, order[:, :5, :], float("nan"))
+            return m
         raise ValueError(kind)
 
     kinds = ["randn", "tie32", "tie64", "uniform-sea-random", "uniform-sea-prefix",
-             "zero-sea", "nonuniform-sea"]
+             "zero-sea", "nonuniform-sea", "signed-zero-sea", "nan-sprinkled"]
     blob = {}
     for kind in kinds:
         m = build(kind).to(torch.bfloat16)          # bf16 path is the exact-index contract

@@ -120,6 +120,48 @@ def test_topk_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
     assert got2.data_ptr() == out.data_ptr() and torch.equal(out, got)
 
 
+@pytest.mark.parametrize("H,K,T,nvp,topk,fb,fe,dt", [
+    (1, 256, 32768, 256, 16, 0, 0, torch.float32),     # the sparse-prefill shape: one chunk of 256 pages
+    (1, 256, 28416, 200, 16, 2, 3, torch.float32),     # just enough token blocks, forced pages
+    (2, 384, 16384, 300, 16, 0, 0, torch.bfloat16),    # two chunks, bf16 scores
+    (4, 768, 8192, 700, 32, 1, 2, torch.float32),      # three chunks, top-32 (no group-maxima bound)
+    (2, 128, 16388, 128, 8, 0, 1, torch.float32),      # top-8, a ragged last token block
+    (1, 1280, 30000, 1100, 16, 0, 0, torch.bfloat16),  # five chunks
+])
+def test_topk_filter_kernel_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
+    """Inputs with enough token blocks to fill the GPU take the filtering kernel (a warp per 32 tokens,
+    candidates above a running threshold only): quantised scores (ties everywhere), a causal -inf
+    tail per token, signed zeros and NaNs sprinkled in."""
+    api = _api()
+    g = gen(7 * H + K + T)
+    m = torch.randn(H, K, T, generator=g)
+    m = (m * 4).round() / 4                                            # many exact ties, +0.0 and -0.0 both occur
+    # causal shape: token t sees pages <= t * nvp / T (at least one); the rest is -inf
+    vis = (torch.arange(T) * nvp // T + 1).view(1, 1, T)
+    m = torch.where(torch.arange(K).view(1, K, 1) < vis, m, torch.tensor(-float("inf")))
+    m[:, nvp:, :] = -float("inf")
+    nan_at = torch.rand(H, K, T, generator=g) < 0.001
+    m = torch.where(nan_at & ~torch.isinf(m), torch.tensor(float("nan")), m).to(dt)
+    ref = orc.topk_select(m.float(), topk, nvp, fb, fe)
+    got = api.sparse_topk_select(m.to(DEV), topk, num_valid_pages=nvp, force_begin_blocks=fb, force_end_blocks=fe)
+    assert torch.equal(got.cpu(), ref)
+
+
+def test_topk_filter_kernel_golden_distributions_bitexact():
+    """The upstream tie distributions (and the signed-zero / NaN ones), repeated along the token axis
+    until the input is large enough for the filtering kernel."""
+    api = _api()
+    z = load_golden("topk_dist.npz")
+    for kind in sorted(k[:-3] for k in z.files if k.endswith("_in")):
+        m = from_bf16_bits(z[kind + "_in"])                            # [4, 512, 8]
+        rep = 1024
+        big = m.repeat(1, 1, rep)                                      # token t of the copy = token t % 8
+        want = torch.from_numpy(z[kind + "_out"]).repeat(rep, 1, 1)
+        for dt in (torch.bfloat16, torch.float32):
+            got = api.sparse_topk_select(big.to(dt).to(DEV), 16, num_valid_pages=m.shape[1])
+            assert torch.equal(got.cpu(), want), (kind, dt)
+
+
 def test_topk_causal_minus_inf_rows():
     """Rows with fewer than k finite scores take -inf pages in ascending index order, never -1."""
     api = _api()

@@ -63,7 +63,7 @@ def test_sparse_attention_matches_upstream_sparse_ref():
 def test_topk_matches_upstream_contract():
     z = load_golden("topk_dist.npz")
     kinds = sorted(k[:-3] for k in z.files if k.endswith("_in"))
-    assert len(kinds) == 7
+    assert len(kinds) == 9 and "signed_zero_sea" in kinds and "nan_sprinkled" in kinds
     for kind in kinds:
         m = from_bf16_bits(z[kind + "_in"]).float()
         got = orc.topk_select(m, 16, num_valid_pages=m.shape[1])
