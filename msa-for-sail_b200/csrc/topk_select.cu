@@ -119,147 +119,122 @@ __device__ __forceinline__ void emit_ascending(const u64 (&key)[TOPK], int32_t* 
 // ------------------------------------------------------------------------------------------------
 // Prefill-sized inputs: filter first, sort only what survives.
 //
-// A warp owns 32 consecutive tokens (lane = token) and walks the pages in chunks of 256.  A chunk
-// [256 pages][32 tokens] is copied into shared memory with 16-byte cp.async (coalesced rows), then
-//   pass A (first chunk): 16 running maxima over the pages p % 16 == g; their minimum thr0 is a lower
-//          bound of the TOPK-th best score (16 distinct pages reach it), so a score below it is out;
+// A warp owns 32 consecutive tokens (lane = token: every page row is one coalesced line).
+//   pass A: 16 running maxima over the pages p % 16 == g of the first 256 pages; their minimum thr0 is
+//           a lower bound of the TOPK-th best score (16 distinct pages reach it), so a score below it
+//           is out (TOPK 8 / 4 fold the maxima pairwise first; TOPK 32 skips the pass);
 //   pass B: a page is a candidate iff !(v < thr0) && !(v <= thr), thr = the score of the list's last
-//          entry (NaN while the list is not full: everything passes).  Both tests are single float
-//          compares, exact with respect to the key order: an equal score loses to the earlier page
-//          that is already in the list, -0.0 == +0.0, and NaN (which ranks first) passes both.
-//          Candidates are appended to a small per-lane buffer of page numbers; when any lane of the
-//          warp holds 5 or more, all lanes fold their (at most 8) candidates into their sorted list
-//          with fixed compare-exchange networks on the exact 64-bit keys, and thr is refreshed.
-// On the configuration this is sized for (256 pages, top 16) about 30 of the 256 scores of a row are
-// ever sorted; the rest cost one load and two compares.  One read of the scores, no workspace.
+//           entry (NaN while the list is not full: everything passes).  Both tests are single float
+//           compares, exact with respect to the key order: an equal score loses to the earlier page
+//           that is already in the list, -0.0 == +0.0, and NaN (which ranks first) passes both.
+//           Candidates are appended to a per-lane buffer of page numbers in shared memory; when any
+//           lane of the warp holds more than 16, all lanes fold theirs into their sorted list with
+//           fixed compare-exchange networks on the exact 64-bit keys, and thr is refreshed.
+// Pass B re-reads what pass A read (from L2: a warp's 256 x 128 bytes were fetched microseconds before);
+// its loads run one block of 16 pages ahead of the compares.  On the shape this is sized for (256 pages,
+// top 16) some 35 of the 256 scores of a row are ever sorted; the rest cost a load and two compares.
+// No shared-memory staging of the scores, so 16 warps per SM hide the latencies; no workspace.
 // ------------------------------------------------------------------------------------------------
-constexpr int kFilterChunk = 256;                // pages per shared-memory chunk
-constexpr int kFilterBuf = 8;                    // candidate slots per lane
-constexpr int kFilterWarps = 2;
-
-template <typename T>
-__device__ __forceinline__ float score_to_float(T v) { return static_cast<float>(v); }
+constexpr int kFilterSlots = 32;                 // candidate slots per lane
+constexpr int kFilterFold = 16;                  // candidates folded per network pass
+constexpr int kFilterWarps = 4;
+constexpr int kFilterBoundPages = 256;           // pages pass A looks at
 
 template <int TOPK, typename T>
-__global__ void __launch_bounds__(kFilterWarps * 32, 3)
+__global__ void __launch_bounds__(kFilterWarps * 32, 4)
 topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles,
                    int total_q, int nvp, int force_begin, int force_end_start) {
-  static_assert(TOPK >= kFilterBuf && TOPK <= 32, "list sizes");
-  constexpr int E = 16 / sizeof(T);              // scores per 16-byte copy
-  constexpr int LPR = 32 / E;                    // lanes that cover one 32-token row
-  constexpr int RPI = 32 / LPR;                  // rows per warp-wide copy instruction
-  constexpr int TILE_BYTES = kFilterChunk * 32 * sizeof(T);
-  extern __shared__ __align__(16) unsigned char fsm[];
+  __shared__ uint16_t s_buf[kFilterWarps][kFilterSlots * 32];                    // [slot][lane]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  T* tile = reinterpret_cast<T*>(fsm + warp * (TILE_BYTES + kFilterBuf * 32 * 2));
-  uint16_t* buf = reinterpret_cast<uint16_t*>(reinterpret_cast<unsigned char*>(tile) + TILE_BYTES);   // [slot][lane]
+  uint16_t* buf = s_buf[warp];
   const int tok_blocks = (total_q + 31) / 32;
   const long long wid = static_cast<long long>(blockIdx.x) * kFilterWarps + warp;
   if (wid >= static_cast<long long>(tok_blocks) * num_heads) return;            // warp-uniform; warps share nothing
   const int head = static_cast<int>(wid / tok_blocks);
-  const int t0 = static_cast<int>(wid % tok_blocks) * 32;
-  const int t = t0 + lane;
-  const T* base = scores + static_cast<size_t>(head) * max_k_tiles * total_q + t0;
+  const int t = static_cast<int>(wid % tok_blocks) * 32 + lane;
+  // a lane past the last token reads the last token's column and stores nothing
+  const T* col = scores + static_cast<size_t>(head) * max_k_tiles * total_q + min(t, total_q - 1);
   const bool any_forced = force_begin > 0 || force_end_start < nvp;
+  auto load = [&](int page) -> float {
+    float v = static_cast<float>(col[static_cast<size_t>(page) * total_q]);
+    if (any_forced && (page < force_begin || page >= force_end_start)) v = 3.402823466e+38f;   // ranks as FLT_MAX
+    return v;
+  };
 
   TopList<TOPK> top;
   top.init();
   float thr = __uint_as_float(0x7FFFFFFFu);       // NaN: nothing is rejected while the list is not full
   int cnt = 0;
 
-  auto value = [&](int r, int page) -> float {    // score of chunk row r (= page) for this lane's token
-    float v = score_to_float(tile[r * 32 + lane]);
-    if (any_forced && (page < force_begin || page >= force_end_start)) v = 3.402823466e+38f;   // ranks as FLT_MAX
-    return v;
+  auto fold16 = [&](int s0) {                     // all lanes: buffered candidates [s0, s0 + 16) -> sorted list
+    u64 c[kFilterFold];
+#pragma unroll
+    for (int s2 = 0; s2 < kFilterFold; ++s2) {
+      const int pg = min(static_cast<int>(buf[(s0 + s2) * 32 + lane]), nvp - 1);   // stale slots hold older pages
+      const float v = load(pg);
+      c[s2] = s0 + s2 < cnt ? ((static_cast<u64>(ord_key(v)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pg))) : 0ull;
+    }
+    TopList<kFilterFold>::sort_desc(c);
+    u64 blk[TOPK];                                // the best min(TOPK, 16) candidates, zero padded
+#pragma unroll
+    for (int i = 0; i < TOPK; ++i) blk[i] = i < kFilterFold ? c[i] : 0ull;
+    top.merge_sorted(blk);
   };
-  auto fold = [&](int k0) {                       // all lanes: buffered candidates -> sorted list
-    u64 blk[TOPK];
-#pragma unroll
-    for (int s2 = 0; s2 < TOPK; ++s2) blk[s2] = 0ull;
-#pragma unroll
-    for (int s2 = 0; s2 < kFilterBuf; ++s2) {
-      const int pg = buf[s2 * 32 + lane];          // stale slots hold in-range pages of this or an earlier chunk
-      const int r = min(max(pg - k0, 0), kFilterChunk - 1);
-      const float v = value(r, pg);
-      blk[s2] = s2 < cnt ? ((static_cast<u64>(ord_key(v)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pg))) : 0ull;
-    }
-    {                                             // descending bitonic sort of the first kFilterBuf entries
-      u64 (&v8)[kFilterBuf] = reinterpret_cast<u64 (&)[kFilterBuf]>(blk);
-      TopList<kFilterBuf>::sort_desc(v8);
-    }
-    top.merge_sorted(blk);                        // entries kFilterBuf.. of blk are 0: compile-time no-ops
+  auto fold_all = [&]() {
+    fold16(0);
+    if (__any_sync(0xffffffffu, cnt > kFilterFold)) fold16(kFilterFold);
     cnt = 0;
     thr = ord_to_float(static_cast<uint32_t>(top.key[TOPK - 1] >> 32));
   };
 
 #pragma unroll 1
-  for (int i = lane; i < kFilterBuf * 32; i += 32) buf[i] = 0;
-  for (int k0 = 0; k0 < nvp; k0 += kFilterChunk) {
-    const int np = min(kFilterChunk, nvp - k0);
-    // ---- copy the chunk: row r of the tile = page k0 + r, 32 tokens ----
-    {
-      const int sub = lane / LPR, c0 = (lane % LPR) * E;
-      const bool col_ok = t0 + c0 < total_q;      // total_q is a multiple of E: a 16-byte piece is in or out as a whole
-      for (int r0 = 0; r0 < np; r0 += RPI) {
-        const int r = r0 + sub;
-        const bool ok = col_ok && r < np;
-        const T* src = base + static_cast<size_t>(k0 + (ok ? r : 0)) * total_q + (ok ? c0 : 0);
-        if (r < kFilterChunk) cp_async16(smem_u32(tile + r * 32 + c0), src, ok);
-      }
-      cp_async_commit();
-      cp_async_wait<0>();
-      __syncwarp();
+  for (int i = lane; i < kFilterSlots * 32; i += 32) buf[i] = 0;
+  __syncwarp();
+
+  // ---- pass A: a lower bound of the TOPK-th best from 16 interleaved group maxima ----
+  float thr0 = -INFINITY;
+  if (TOPK <= 16 && nvp >= 2 * TOPK) {
+    const int na = min(nvp, kFilterBoundPages);
+    float gm[16];
+#pragma unroll
+    for (int g = 0; g < 16; ++g) gm[g] = -INFINITY;
+    for (int p0 = 0; p0 < na; p0 += 16) {
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        if (p0 + u < na) gm[u] = fmaxf(gm[u], load(p0 + u));
     }
-    // ---- pass A: a lower bound of the TOPK-th best from 16 interleaved group maxima ----
-    float thr0 = -INFINITY;
-    if (k0 == 0 && np >= 2 * TOPK) {
-      float gm[16];
+    // TOPK distinct pages must reach the bound: fold the 16 maxima in groups of 16 / TOPK (each group's
+    // maximum is one real score) and take the smallest
+    constexpr int STEP = TOPK <= 16 ? 16 / TOPK : 1;
+    thr0 = INFINITY;
 #pragma unroll
-      for (int g = 0; g < 16; ++g) gm[g] = -INFINITY;
-      for (int p0 = 0; p0 < np; p0 += 16) {
+    for (int g = 0; g < 16; g += STEP) {
+      float m = gm[g];
 #pragma unroll
-        for (int u = 0; u < 16; ++u)
-          if (p0 + u < np) gm[u] = fmaxf(gm[u], value(p0 + u, p0 + u));
-      }
-      // TOPK distinct pages must reach the bound: the TOPK largest of the 16 maxima do (TOPK <= 16),
-      // two per group would be needed beyond that
-      if (TOPK <= 16) {
-        float lo[16];
-#pragma unroll
-        for (int g = 0; g < 16; ++g) lo[g] = gm[g];
-        if (TOPK == 16) {
-          thr0 = lo[0];
-#pragma unroll
-          for (int g = 1; g < 16; ++g) thr0 = fminf(thr0, lo[g]);
-        } else {                                  // TOPK 4 / 8: fold the 16 maxima pairwise, keeping the smaller of
-          constexpr int STEP = 16 / TOPK;         // each group of 16 / TOPK -- TOPK values, each a real score
-          thr0 = INFINITY;
-#pragma unroll
-          for (int g = 0; g < 16; g += STEP) {
-            float m = lo[g];
-#pragma unroll
-            for (int e2 = 1; e2 < STEP; ++e2) m = fmaxf(m, lo[g + e2]);
-            thr0 = fminf(thr0, m);
-          }
-        }
-      }
+      for (int e2 = 1; e2 < STEP; ++e2) m = fmaxf(m, gm[g + e2]);
+      thr0 = fminf(thr0, m);
     }
-    // ---- pass B: filter, buffer, fold ----
-    for (int p0 = 0; p0 < np; p0 += 4) {
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = p0 + u;
-        if (r < np) {
-          const float v = value(r, k0 + r);
-          const bool cand = !(v < thr0) && !(v <= thr);
-          if (cand) { buf[cnt * 32 + lane] = static_cast<uint16_t>(k0 + r); ++cnt; }
-        }
-      }
-      if (__any_sync(0xffffffffu, cnt > kFilterBuf - 4)) fold(k0);
-    }
-    if (__any_sync(0xffffffffu, cnt > 0)) fold(k0);
-    __syncwarp();                                 // the tile is overwritten by the next chunk's copies
   }
+
+  // ---- pass B: filter, buffer, fold; the loads of block p0 + 16 are in flight while block p0 is compared ----
+  float cur[16];
+#pragma unroll
+  for (int u = 0; u < 16; ++u) cur[u] = u < nvp ? load(u) : 0.f;
+  for (int p0 = 0; p0 < nvp; p0 += 16) {
+    float nxt[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) nxt[u] = p0 + 16 + u < nvp ? load(p0 + 16 + u) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const float v = cur[u];
+      const bool cand = p0 + u < nvp && !(v < thr0) && !(v <= thr);
+      if (cand) { buf[cnt * 32 + lane] = static_cast<uint16_t>(p0 + u); ++cnt; }
+    }
+    if (__any_sync(0xffffffffu, cnt > kFilterFold)) fold_all();
+#pragma unroll
+    for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
+  }
+  if (__any_sync(0xffffffffu, cnt > 0)) fold_all();
   if (t < total_q) emit_ascending<TOPK>(top.key, out + (static_cast<size_t>(t) * num_heads + head) * TOPK);
 }
 
@@ -424,18 +399,13 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
   }
   const int tok_blocks = (T_ + 31) / 32;
   const long long ctas = static_cast<long long>(tok_blocks) * H;
-  // enough token blocks to fill the GPU, rows that 16-byte copies can address, page numbers that fit
-  // the 16-bit candidate buffer: the filtering kernel
-  constexpr int kE = 16 / sizeof(T);
-  if (ctas >= 148LL * 3 * kFilterWarps && T_ % kE == 0 && (reinterpret_cast<uintptr_t>(scores) & 15) == 0 &&
-      nvp <= 65535 && TOPK >= kFilterBuf) {
-    auto fk = topk_filter_kernel<(TOPK >= kFilterBuf ? TOPK : kFilterBuf), T>;
-    const size_t fsmem = kFilterWarps * (kFilterChunk * 32 * sizeof(T) + kFilterBuf * 32 * 2);
+  // enough token blocks to give every SM several warps, page numbers that fit the 16-bit candidate
+  // buffer: the filtering kernel
+  if (ctas >= 148LL * 8 && nvp <= 65535) {
     const long long fctas = (ctas + kFilterWarps - 1) / kFilterWarps;
     if (fctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
-    if (cudaFuncSetAttribute(fk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fsmem)) != cudaSuccess)
-      return MSA_ERR_LAUNCH;
-    fk<<<static_cast<unsigned>(fctas), kFilterWarps * 32, fsmem, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
+    topk_filter_kernel<TOPK, T><<<static_cast<unsigned>(fctas), kFilterWarps * 32, 0, stream>>>(scores, out, H, K, T_, nvp,
+                                                                                              fb, fe_start);
     return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
   }
   // enough slices to put ~16 warps on every SM, bounded by the pages there are to scan

@@ -66,7 +66,7 @@ def test_msa_prefill_parity_sample_with_page_offsets(hq, hk, topk):
     wl = bench.setup_msa_prefill(msa, torch.device("cuda:0"), 5, b=2, t=4096, hq=hq, hk=hk, topk=topk)
     wl["step"]()
     r = wl["parity"]()
-    assert r["topk_exact"] and r["max_abs"] <= 2e-2 and r["cos_min"] >= 0.9999
+    assert r["topk_exact"] and r["max_abs"] <= 2e-2 and r["cos"] >= 0.9999
 
 
 @pytest.mark.parametrize("fp8", [True, False])

@@ -121,15 +121,16 @@ def test_topk_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
 
 
 @pytest.mark.parametrize("H,K,T,nvp,topk,fb,fe,dt", [
-    (1, 256, 32768, 256, 16, 0, 0, torch.float32),     # the sparse-prefill shape: one chunk of 256 pages
-    (1, 256, 28416, 200, 16, 2, 3, torch.float32),     # just enough token blocks, forced pages
-    (2, 384, 16384, 300, 16, 0, 0, torch.bfloat16),    # two chunks, bf16 scores
-    (4, 768, 8192, 700, 32, 1, 2, torch.float32),      # three chunks, top-32 (no group-maxima bound)
-    (2, 128, 16388, 128, 8, 0, 1, torch.float32),      # top-8, a ragged last token block
-    (1, 1280, 30000, 1100, 16, 0, 0, torch.bfloat16),  # five chunks
+    (1, 256, 40000, 256, 16, 0, 0, torch.float32),     # the sparse-prefill shape: 256 pages, top-16
+    (1, 256, 37900, 200, 16, 2, 3, torch.float32),     # just enough token blocks, forced pages
+    (2, 384, 19000, 300, 16, 0, 0, torch.bfloat16),    # more pages than the bound pass looks at, bf16 scores
+    (4, 768, 9500, 700, 32, 1, 2, torch.float32),      # top-32 (no group-maxima bound)
+    (2, 128, 19012, 128, 8, 0, 1, torch.float32),      # top-8, a ragged last token block
+    (2, 128, 19012, 100, 4, 1, 0, torch.bfloat16),     # top-4
+    (1, 1280, 38000, 1100, 16, 0, 0, torch.bfloat16),  # long rows
 ])
 def test_topk_filter_kernel_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
-    """Inputs with enough token blocks to fill the GPU take the filtering kernel (a warp per 32 tokens,
+    """Inputs with at least 1 184 blocks of 32 tokens take the filtering kernel (a warp per 32 tokens,
     candidates above a running threshold only): quantised scores (ties everywhere), a causal -inf
     tail per token, signed zeros and NaNs sprinkled in."""
     api = _api()
@@ -154,7 +155,7 @@ def test_topk_filter_kernel_golden_distributions_bitexact():
     z = load_golden("topk_dist.npz")
     for kind in sorted(k[:-3] for k in z.files if k.endswith("_in")):
         m = from_bf16_bits(z[kind + "_in"])                            # [4, 512, 8]
-        rep = 1024
+        rep = 1200
         big = m.repeat(1, 1, rep)                                      # token t of the copy = token t % 8
         want = torch.from_numpy(z[kind + "_out"]).repeat(rep, 1, 1)
         for dt in (torch.bfloat16, torch.float32):
