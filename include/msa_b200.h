@@ -38,6 +38,9 @@ extern "C" {
 /* device status word values (written only when MsaFmhaParams.status != NULL) */
 #define MSA_STATUS_OK        0
 #define MSA_STATUS_TIMEOUT   1   /* a bounded wait inside a kernel gave up       */
+#define MSA_STATUS_BOUNDS    2   /* bounds-checked build only (-DMSA_BOUNDS_CHECK): an index read from a
+                                    caller's table (work item, page table, token -> batch map) was out of
+                                    range; it was clamped into range before use                            */
 
 typedef void* msa_stream_t;      /* a cudaStream_t */
 

@@ -19,6 +19,16 @@ Full (O and max_score), OnlyScore (max_score only), Sparse (O over kv_block_num 
     python run_msa.py --format "<line>"            # run once
     python run_msa.py --format "<line>" --bench    # time it; TFLOP/s and GB/s against the B200 peaks
     python run_msa.py --caselist cases.txt [--case_idx N]
+
+``--sweep`` prints the tables of the upstream sweep benchmark (benchmarks/bench_sparse_attention_ops.py:
+341-439): sections prefill (ragged dense, head presets TP1 64/4, TP2 32/2, TP4 16/1), paged_prefill,
+sparse_prefill (the first top-k pages for every token), decode (4 query tokens, 64/4 heads), paged_decode,
+sparse_decode (8 query tokens; a paged dense row and a sparse row per shape), with the upstream columns; ``-o``
+writes the same rows tab-separated under the upstream header.  Each row is timed with a cold L2 (a 256 MB
+buffer is rewritten before every iteration), median and standard deviation over the iterations.
+
+    python run_msa.py --sweep [--sections prefill,sparse_decode] [--dtype bf16|fp8] [--seqs 8192,32768]
+                      [--tp 1,2,4] [--decode-k 8192,65536] [--decode-b 32,64] [--topk 16] [-o sweep.tsv]
 """
 import argparse
 import json
@@ -107,7 +117,8 @@ def flops_and_bytes(cfg):
     return flops, nbytes
 
 
-def build_and_run(cfg, bench=False, iters=20, peaks=None):
+def build_case(cfg):
+    """Random tensors, plan and the call of one case: returns (callable, plan)."""
     import torch
     import msa_for_sail as msa
     dev = "cuda"
@@ -137,7 +148,12 @@ def build_and_run(cfg, bench=False, iters=20, peaks=None):
                               qo_offset=i32(offs) if offs else None, use_fp8_kvcache=fp8,
                               output_maxscore=mode in ("Full", "OnlyScore"),
                               kv_block_num=kbn if mode == "Sparse" else -1)
-    if mode == "Sparse":
+    if mode == "Sparse" and cfg.get("selection") == "first":      # the sweep's choice: pages 0 .. k-1 for every token
+        n_sel = min(kbn, min((kl + page - 1) // page for kl in sk))
+        sel = torch.full((total_q, hk, kbn), -1, dtype=torch.int32, device=dev)
+        sel[:, :, :n_sel] = torch.arange(n_sel, dtype=torch.int32, device=dev)
+        kw["kv_block_indexes"] = sel
+    elif mode == "Sparse":
         rows = []
         for b, (ql, kl) in enumerate(zip(sq, sk)):
             o = offs[b] if offs else kl - ql
@@ -156,6 +172,13 @@ def build_and_run(cfg, bench=False, iters=20, peaks=None):
     def fn():
         return msa.fmha_sail(q, k, v, plan, **kw)
 
+    return fn, plan
+
+
+def build_and_run(cfg, bench=False, iters=20, peaks=None):
+    import torch
+    fn, _ = build_case(cfg)
+    mode, fp8 = cfg["sparse_mode"], cfg["dtype"] in ("fp8", "e4m3")
     out, ms = fn()
     torch.cuda.synchronize()
     print(f"[run_msa] RAN OK [sparse_mode={mode}]: out={None if out is None else tuple(out.shape)} "
@@ -180,6 +203,138 @@ def build_and_run(cfg, bench=False, iters=20, peaks=None):
     return ms_mean
 
 
+# ----------------------------------------------------------------------------------------------
+# sweep tables
+# ----------------------------------------------------------------------------------------------
+SWEEP_SECTIONS = ("prefill", "paged_prefill", "sparse_prefill", "decode", "paged_decode", "sparse_decode")
+TP_HEADS = {1: (64, 4), 2: (32, 2), 4: (16, 1)}            # head presets of the prefill sections
+DECODE_HEADS = (64, 4)
+TSV_HEADER = ["q_len", "kv_len", "dtype", "batch_size", "q_head", "kv_head", "head_dim", "latency_ms", "std_ms",
+              "tflops", "gbs", "mfu_mbu_pct", "predicted_split_speedup_pct"]
+TABLE = [("q_len", 8), ("kv_len", 8), ("dtype", 6), ("bsz", 5), ("h_q", 4), ("h_kv", 5), ("dim", 4), ("lat(ms)", 11),
+         ("std(ms)", 9), ("TFLOPs", 10), ("GB/s", 10), ("MFU/MBU", 9), ("split%", 8)]
+
+
+def sweep_cases(section, dtype="bf16", seqs=(8192, 16384, 32768, 65536, 131072), tp=(1, 2, 4),
+                decode_k=(8192, 16384, 32768, 65536), decode_b=(32, 64, 128), topk=16, output_mode="o"):
+    """The rows of one section: (table title, case dict, rated by bandwidth?)."""
+    mode = {"o": "Off", "full": "Full", "maxscore": "OnlyScore"}[output_mode]
+
+    def case(b, q, k, hq, hk, paged, sparse):
+        return {"dtype": dtype, "batch_size": b, "seqlen_q": [q] * b, "seqlen_k": [k] * b, "qo_offset": [k - q] * b,
+                "num_qo_heads": hq, "num_kv_heads": hk, "head_dim_qk": 128, "head_dim_vo": 128, "num_kv_splits": -1,
+                "is_paged": int(paged), "page_size": 128, "causal": 1, "sparse_mode": "Sparse" if sparse else mode,
+                "kv_block_num": topk if sparse else 0, "selection": "first"}
+
+    if section == "prefill":
+        for t in tp:
+            hq, hk = TP_HEADS[t]
+            for s_ in seqs:
+                yield f"Prefill TP{t} (ragged dense, causal, {dtype})", case(1, s_, s_, hq, hk, False, False), False
+    elif section in ("paged_prefill", "sparse_prefill"):
+        hq, hk = TP_HEADS[1]
+        sparse = section == "sparse_prefill"
+        title = (f"Sparse Prefill TP1 (first top-K, page=128, topk={topk}, {dtype})" if sparse else
+                 f"Paged Prefill TP1 (paged dense, causal, page=128, {dtype})")
+        for s_ in seqs:
+            yield title, case(1, s_, s_, hq, hk, True, sparse), False
+    elif section in ("decode", "paged_decode"):
+        hq, hk = DECODE_HEADS
+        paged = section == "paged_decode"
+        title = (f"Paged Decode (paged dense, MBU, page=128, h={hq}/{hk}, {dtype})" if paged else
+                 f"Decode (ragged dense, MBU, h={hq}/{hk}, {dtype})")
+        for b in decode_b:
+            for k in decode_k:
+                yield title, case(b, 4, k, hq, hk, paged, False), True
+    elif section == "sparse_decode":
+        hq, hk = DECODE_HEADS
+        for b in decode_b:
+            for k in decode_k:
+                for sparse in (False, True):              # a paged dense row, then the sparse row of the same shape
+                    yield (f"Sparse Decode (dense+sparse pairs, MBU, topk={topk}, {dtype})",
+                           case(b, 8, k, hq, hk, True, sparse), True)
+    else:
+        raise ValueError(f"unknown section {section!r}; valid: {', '.join(SWEEP_SECTIONS)}")
+
+
+def sweep_work(cfg):
+    """FLOPs and bytes of a sweep row by the upstream sweep's own formulas
+    (bench_sparse_attention_ops.py:135-140, 313-316): a sparse row counts the keys it reads, unmasked."""
+    b, q, k = cfg["batch_size"], cfg["seqlen_q"][0], cfg["seqlen_k"][0]
+    hq, hk = cfg["num_qo_heads"], cfg["num_kv_heads"]
+    e = 1 if cfg["dtype"] in ("fp8", "e4m3") else 2
+    if cfg["sparse_mode"] == "Sparse":
+        k_eff = min(min(cfg["kv_block_num"], (k + 127) // 128) * 128, k)
+        pairs = q * k_eff
+    else:
+        k_eff = k
+        pairs = q * k - q * (q - 1) // 2
+    flops = b * hq * pairs * (128 + 128) * 2
+    nbytes = b * q * hq * 128 * e + b * k_eff * hk * 128 * e * 2 + b * q * hq * 128 * 2
+    return flops, nbytes
+
+
+def time_cold(fn, dry_ms=200, repeat_ms=1000):
+    """Per-iteration CUDA-event times (ms) with the L2 rewritten before every iteration."""
+    import torch
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+    one = max(e0.elapsed_time(e1), 1e-3)
+    for _ in range(max(1, int(dry_ms / one))):
+        fn()
+    n = max(5, min(2000, int(repeat_ms / one)))
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    for a, b in evs:
+        flush.zero_()
+        a.record(); fn(); b.record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in evs]
+
+
+def run_sweep(args, peaks):
+    import statistics
+    sections = [x.strip() for x in args.sections.split(",") if x.strip()]
+    if "all" in sections:
+        sections = list(SWEEP_SECTIONS)
+    ints = lambda text, default: [int(x) for x in text.split(",")] if text else list(default)
+    kw = dict(dtype=args.dtype, seqs=ints(args.seqs, (8192, 16384, 32768, 65536, 131072)), tp=ints(args.tp, (1, 2, 4)),
+              decode_k=ints(args.decode_k, (8192, 16384, 32768, 65536)), decode_b=ints(args.decode_b, (32, 64, 128)),
+              topk=args.topk, output_mode=args.output_mode)
+    tsv = open(args.output, "w") if args.output else None
+    if tsv:
+        tsv.write("\t".join(TSV_HEADER) + "\n")
+    rule = "-" * (sum(w for _, w in TABLE) + len(TABLE) - 1)
+    peak_tf = peaks["fp8_tflops" if args.dtype == "fp8" else "bf16_tflops"]
+    for section in sections:
+        last_title = None
+        for title, cfg, by_bandwidth in sweep_cases(section, **kw):
+            if title != last_title:
+                print(f"\n{title}\n{rule}\n" + " ".join(f"{n:>{w}}" for n, w in TABLE) + f"\n{rule}", flush=True)
+                last_title = title
+            try:
+                fn, plan = build_case(cfg)
+                times = time_cold(fn, args.dry_run_ms, args.repeat_ms)
+            except Exception as exc:                             # noqa: BLE001  (a row that does not fit is reported, the sweep goes on)
+                sys.stderr.write(f"  row skipped ({cfg['seqlen_q'][0]} x {cfg['seqlen_k'][0]}, b={cfg['batch_size']}): {exc}\n")
+                continue
+            med, std = statistics.median(times), statistics.pstdev(times)
+            flops, nbytes = sweep_work(cfg)
+            tf, gb = flops / med / 1e9, nbytes / med / 1e6
+            rate = gb / peaks["hbm_gbs"] if by_bandwidth else tf / peak_tf
+            split = plan[3].get("predicted_speedup", 1.0)
+            row = [cfg["seqlen_q"][0], cfg["seqlen_k"][0], args.dtype, cfg["batch_size"], cfg["num_qo_heads"],
+                   cfg["num_kv_heads"], 128]
+            cells = [str(x) for x in row] + [f"{med:.4f}", f"{std:.4f}", f"{tf:.2f}", f"{gb:.2f}", f"{rate * 100:.2f}%",
+                                             f"{(split - 1) * 100:.2f}%"]
+            print(" ".join(f"{c:>{w}}" for c, (_, w) in zip(cells, TABLE)), flush=True)
+            if tsv:
+                tsv.write("\t".join([str(x) for x in row] + [f"{med:.4f}", f"{std:.4f}", f"{tf:.4f}", f"{gb:.4f}",
+                                                             f"{rate * 100:.4f}", f"{(split - 1) * 100:.4f}"]) + "\n")
+                tsv.flush()
+    if tsv:
+        tsv.close()
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--format", type=str, default=None, help="one '[MSA] --format=...' line")
@@ -188,7 +343,27 @@ def main():
     ap.add_argument("--bench", action="store_true", help="time the case")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--peaks", type=str, default=None, help="JSON file with bf16_tflops / fp8_tflops / hbm_gbs")
+    ap.add_argument("--sweep", action="store_true", help="print the sweep tables instead of running single cases")
+    ap.add_argument("--sections", type=str, default="all", help="comma-separated: " + ",".join(SWEEP_SECTIONS) + ",all")
+    ap.add_argument("--dtype", choices=["bf16", "fp8"], default="bf16")
+    ap.add_argument("--output_mode", choices=["full", "maxscore", "o"], default="o")
+    ap.add_argument("--seqs", type=str, default=None, help="q = k lengths of the prefill sections")
+    ap.add_argument("--tp", type=str, default=None, help="head presets of the prefill section: 1,2,4")
+    ap.add_argument("--decode-k", dest="decode_k", type=str, default=None, help="KV lengths of the decode sections")
+    ap.add_argument("--decode-b", dest="decode_b", type=str, default=None, help="batch sizes of the decode sections")
+    ap.add_argument("--topk", type=int, default=16, choices=[4, 8, 16, 32])
+    ap.add_argument("--dry-run-ms", dest="dry_run_ms", type=int, default=200)
+    ap.add_argument("--repeat-ms", dest="repeat_ms", type=int, default=1000)
+    ap.add_argument("--output", "-o", type=str, default=None, help="tab-separated copy of the sweep rows")
     args = ap.parse_args()
+    if args.sweep:
+        pk = dict(PEAKS)
+        if args.peaks:
+            with open(args.peaks) as f:
+                raw = json.load(f)
+            pk.update({k: raw[k] for k in PEAKS if k in raw})
+        run_sweep(args, pk)
+        return
     lines = []
     if args.format:
         lines.append(args.format)

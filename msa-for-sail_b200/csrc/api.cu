@@ -1,8 +1,10 @@
 // C ABI front end: argument checks, kernel selection, the host-side dense planner.
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
+#include "nvtx_range.h"
 
 namespace msa {
 int fmha_mma_launch(const MsaFmhaParams& p, cudaStream_t stream);
@@ -15,6 +17,19 @@ int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_sparse_tc_supported(const MsaFmhaParams& p);
 int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int64_t fmha_sparse_tc_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
+int fmha_sparse_fused_launch(const MsaFmhaParams& p, cudaStream_t stream);
+int64_t fmha_sparse_fused_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
+
+// Which schedule sparse prefill runs on: "band" = the persistent kernel that merges its partials while they
+// are still in the L2 (fmha_sparse_fused.cu), "page" = attention kernel + separate merge kernel
+// (fmha_sparse_tc.cu).  Read once from MSA_SPARSE_SCHEDULE.
+static bool sparse_schedule_is_band() {
+  static const bool band = [] {
+    const char* e = getenv("MSA_SPARSE_SCHEDULE");
+    return e != nullptr && e[0] == 'b';
+  }();
+  return band;
+}
 }  // namespace msa
 
 namespace msa {
@@ -68,10 +83,12 @@ int validate_fmha(const MsaFmhaParams& p, bool own_scratch) {
 
 extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
   if (!pp) return MSA_ERR_BAD_ARG;
+  msa::NvtxRange range("msa_fmha_fwd");
   const MsaFmhaParams& p = *pp;
   if (const int rc = msa::validate_fmha(p, false)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (msa::fmha_sparse_tc_supported(p)) return msa::fmha_sparse_tc_launch(p, stream);
+  if (msa::fmha_sparse_tc_supported(p))
+    return msa::sparse_schedule_is_band() ? msa::fmha_sparse_fused_launch(p, stream) : msa::fmha_sparse_tc_launch(p, stream);
   if (msa::score_gemv_supported(p)) return msa::score_gemv_launch(p, stream);
   if (msa::fmha_decode_tc_supported(p)) return msa::fmha_decode_tc_launch(p, stream);
   if (msa::fmha_tc_supported(p)) return msa::fmha_tc_launch(p, stream);
@@ -81,6 +98,7 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
 extern "C" int msa_plan_dense(const MsaPlanArgs* a, MsaWorkItem* work, int32_t capacity, int32_t* splits_per_row,
                               int32_t* max_splits_out) {
   if (!a || !a->qo_len || !a->kv_len || !a->qo_offset || (!work && capacity > 0)) return MSA_ERR_BAD_ARG;
+  msa::NvtxRange range("msa_plan_dense");
   if (a->block_m != 16 && a->block_m != 64 && a->block_m != 128 && a->block_m != 256) return MSA_ERR_BAD_ARG;
   if (a->num_qo_heads <= 0 || a->num_kv_heads <= 0 || a->num_qo_heads % a->num_kv_heads) return MSA_ERR_BAD_ARG;
   const int G = a->pack;
@@ -154,7 +172,8 @@ extern "C" int64_t msa_sparse_workspace_bytes(int64_t total_q, int32_t num_qo_he
   if (total_q < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads || kv_block_num <= 0 ||
       num_logical_pages < 0)
     return MSA_ERR_BAD_ARG;
-  return msa::fmha_sparse_tc_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages);
+  return std::max(msa::fmha_sparse_tc_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages),
+                  msa::fmha_sparse_fused_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages));
 }
 
 extern "C" const char* msa_status_string(int code) {

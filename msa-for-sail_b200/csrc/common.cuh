@@ -16,6 +16,21 @@ constexpr int kKvTile = 128;    // keys per KV tile == max_score granularity
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// Range check of an index that a kernel read from a caller's table and is about to turn into an address
+// (upstream: FMHA_GMEM_CHECK=1, csrc/gmem_bounds_check.h:27-69, which prints and returns 0).  In the
+// bounds-checked build (-DMSA_BOUNDS_CHECK, libmsa_b200_check.so) a value outside [lo, hi) is clamped
+// into the range and the first violation is recorded in the caller's status word -- no printf, no trap,
+// the launch completes; in the shipped build the function is the identity.
+#ifdef MSA_BOUNDS_CHECK
+__device__ __forceinline__ int chk(int v, int lo, int hi, int32_t* status) {
+  if (v >= lo && v < hi) return v;
+  if (status) atomicCAS(status, MSA_STATUS_OK, MSA_STATUS_BOUNDS);
+  return hi > lo ? min(max(v, lo), hi - 1) : lo;
+}
+#else
+__device__ __forceinline__ int chk(int v, int, int, int32_t*) { return v; }
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -36,6 +36,15 @@ namespace {
 
 using namespace tc;
 
+// The row sum is taken over the probabilities AS THE MMA SEES THEM (rounded to e4m3 / bf16), so that the
+// weights of a row add up to its normaliser exactly: a row dominated by one key then reproduces that key's V
+// whatever the rounding of its probability (with the unrounded sum the rounding error of the largest
+// probability, up to 2^-4 in e4m3, goes straight into O).
+__device__ __forceinline__ float2 e4m3x2_as_float2(uint16_t x) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(x), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+
 constexpr int BM = 128, BN = 128;
 constexpr int SUB_BYTES = BM * 128;             // one [128 rows][128 bytes] swizzled sub-tile
 constexpr int NTHREADS = 224;
@@ -141,7 +150,8 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const int32_t* blocks = nullptr;
   if (!sparse) {
     const MsaWorkItem w = p.work[blockIdx.x];
-    b = w.batch; head0 = w.head0; tb = w.kv_tile_begin; te = w.kv_tile_end; split = w.split;
+    b = chk(w.batch, 0, p.batch, p.status); head0 = chk(w.head0, 0, p.num_qo_heads, p.status);
+    tb = w.kv_tile_begin; te = w.kv_tile_end; split = chk(w.split, 0, p.num_splits, p.status);
     i_base = 0;
     ntok = p.qo_start[b + 1] - p.qo_start[b];
   } else {
@@ -156,7 +166,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     te = min(p.kv_block_num, tb + per);
     // independent of the batch item: in flight together with the loads below that depend on it
     if (warp == PRODUCER_WARP && tb + lane < te) blk_first = blocks[tb + lane];
-    b = p.token_batch[t];
+    b = chk(p.token_batch[t], 0, p.batch, p.status);
     head0 = kvh_s * h_r;
     i_base = t - p.qo_start[b];
     ntok = 1;
@@ -207,7 +217,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         }
         const int pos = n + incl - nu;
         if (nu > 0 && pos + nu <= MAX_SPARSE_TILES * UPP) {
-          const int ph = p.kv_indices[page_base + blk];
+          const int ph = chk(p.kv_indices[page_base + blk], 0, static_cast<int>(p.kv_extent), p.status);
           for (int u = 0; u < nu; ++u) { s_tiles[pos + u] = blk * UPP + u; s_phys[pos + u] = ph; }
         }
         n += __shfl_sync(0xffffffffu, incl, 31);
@@ -258,8 +268,8 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     int phys_cur = 0, phys_next = 0;
     const int n_pages = (n_tiles + UPP - 1) / UPP;
     if (!sparse) {
-      phys_cur = lane < n_pages ? p.kv_indices[page_base + tb + lane] : 0;
-      phys_next = 32 + lane < n_pages ? p.kv_indices[page_base + tb + 32 + lane] : 0;
+      phys_cur = lane < n_pages ? chk(p.kv_indices[page_base + tb + lane], 0, static_cast<int>(p.kv_extent), p.status) : 0;
+      phys_next = 32 + lane < n_pages ? chk(p.kv_indices[page_base + tb + 32 + lane], 0, static_cast<int>(p.kv_extent), p.status) : 0;
     }
     uint32_t fix_phase = 0;
     bool alive = do_k || do_v;
@@ -270,7 +280,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       const int pg = j / UPP;                                // dense: page index within this item
       if (!sparse && j > 0 && (j % (32 * UPP)) == 0) {
         phys_cur = phys_next;
-        phys_next = pg + 32 + lane < n_pages ? p.kv_indices[page_base + tb + pg + 32 + lane] : 0;
+        phys_next = pg + 32 + lane < n_pages ? chk(p.kv_indices[page_base + tb + pg + 32 + lane], 0, static_cast<int>(p.kv_extent), p.status) : 0;
       }
       const int phys = sparse ? s_phys[j] : __shfl_sync(0xffffffffu, phys_cur, pg & 31);
       const int valid_rows = min(TK, kv_len - key0);
@@ -491,9 +501,10 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
             const float p1 = exp2_fast(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -msafe));
             const float p2 = exp2_fast(fmaf(__uint_as_float(sv[e + 2]), scale_log2, -msafe));
             const float p3 = exp2_fast(fmaf(__uint_as_float(sv[e + 3]), scale_log2, -msafe));
-            l0 += p0 + p2; l1 += p1 + p3;
             const uint16_t lo = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
             const uint16_t hi = __nv_cvt_float2_to_fp8x2(make_float2(p2, p3), __NV_SATFINITE, __NV_E4M3);
+            const float2 ra = e4m3x2_as_float2(lo), rb = e4m3x2_as_float2(hi);
+            l0 += ra.x + rb.x; l1 += ra.y + rb.y;
             pk[e >> 2] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
           }
         } else {
@@ -501,8 +512,9 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
           for (int e = 0; e < CW; e += 2) {
             const float p0 = exp2_fast(fmaf(__uint_as_float(sv[e]), scale_log2, -msafe));
             const float p1 = exp2_fast(fmaf(__uint_as_float(sv[e + 1]), scale_log2, -msafe));
-            l0 += p0; l1 += p1;
-            pk[e >> 1] = pack2<false>(p0, p1);
+            const uint32_t pr = pack2<false>(p0, p1);
+            l0 += __uint_as_float(pr << 16); l1 += __uint_as_float(pr & 0xffff0000u);
+            pk[e >> 1] = pr;
           }
         }
         // P of this quadrant's rows: own keys, zero for the other three quarters of the tile
@@ -600,9 +612,10 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
             const float p1 = exp2_fast(fmaf(__uint_as_float(sv[c][e + 1]), scale_log2, -msafe));
             const float p2 = exp2_fast(fmaf(__uint_as_float(sv[c][e + 2]), scale_log2, -msafe));
             const float p3 = exp2_fast(fmaf(__uint_as_float(sv[c][e + 3]), scale_log2, -msafe));
-            l0 += p0 + p2; l1 += p1 + p3;
             const uint16_t lo = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
             const uint16_t hi = __nv_cvt_float2_to_fp8x2(make_float2(p2, p3), __NV_SATFINITE, __NV_E4M3);
+            const float2 ra = e4m3x2_as_float2(lo), rb = e4m3x2_as_float2(hi);
+            l0 += ra.x + rb.x; l1 += ra.y + rb.y;
             pk[e >> 2] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
           }
           tmem_st8(tS + c * 8, pk);
@@ -612,8 +625,9 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
           for (int e = 0; e < 32; e += 2) {
             const float p0 = exp2_fast(fmaf(__uint_as_float(sv[c][e]), scale_log2, -msafe));
             const float p1 = exp2_fast(fmaf(__uint_as_float(sv[c][e + 1]), scale_log2, -msafe));
-            l0 += p0; l1 += p1;
-            pk[e >> 1] = pack2<false>(p0, p1);
+            const uint32_t pr = pack2<false>(p0, p1);
+            l0 += __uint_as_float(pr << 16); l1 += __uint_as_float(pr & 0xffff0000u);
+            pk[e >> 1] = pr;
           }
           tmem_st16(tS + c * 16, pk);
         }

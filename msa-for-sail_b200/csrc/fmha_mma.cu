@@ -69,7 +69,8 @@ fmha_mma_kernel(const __grid_constant__ MsaFmhaParams p) {
   if (!sparse) {
     if (static_cast<int>(blockIdx.x) >= p.num_work) return;
     const MsaWorkItem w = p.work[blockIdx.x];
-    b = w.batch; head0 = w.head0; row0 = w.row0; tb = w.kv_tile_begin; te = w.kv_tile_end; split = w.split;
+    b = chk(w.batch, 0, p.batch, p.status); head0 = chk(w.head0, 0, p.num_qo_heads, p.status); row0 = w.row0;
+    tb = w.kv_tile_begin; te = w.kv_tile_end; split = chk(w.split, 0, p.num_splits, p.status);
     i_base = 0;
     rows_total = min((p.qo_start[b + 1] - p.qo_start[b]) * G, w.row0 + w.num_rows);
   } else {
@@ -79,7 +80,7 @@ fmha_mma_kernel(const __grid_constant__ MsaFmhaParams p) {
     const int kvh_s = idx % p.num_kv_heads;
     const int t = idx / p.num_kv_heads;
     if (t >= p.total_q) return;
-    b = p.token_batch[t];
+    b = chk(p.token_batch[t], 0, p.batch, p.status);
     head0 = kvh_s * h_r; row0 = 0; rows_total = G;
     i_base = t - p.qo_start[b];
     blocks = p.kv_block_indexes + static_cast<int64_t>(t) * p.kbi_stride_tok + static_cast<int64_t>(kvh_s) * p.kbi_stride_head;
@@ -155,7 +156,7 @@ fmha_mma_kernel(const __grid_constant__ MsaFmhaParams p) {
         if (ps > 0) {
           const int lp = sparse ? s.lpage : pos / ps;
           const int in_page = sparse ? r : pos - lp * ps;
-          const int64_t pg = p.kv_indices[page_base + lp];
+          const int64_t pg = chk(p.kv_indices[page_base + lp], 0, static_cast<int>(p.kv_extent), p.status);
           ko = pg * p.k_stride_page + static_cast<int64_t>(kvh) * p.k_stride_head + static_cast<int64_t>(in_page) * p.k_stride_tok;
           vo = pg * p.v_stride_page + static_cast<int64_t>(kvh) * p.v_stride_head + static_cast<int64_t>(in_page) * p.v_stride_tok;
         } else {

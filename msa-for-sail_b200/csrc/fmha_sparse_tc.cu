@@ -127,6 +127,7 @@ struct IndexArgs {
   const int32_t* kbi; int64_t kbi_stride_tok, kbi_stride_head;
   const int32_t* token_batch; const int32_t* qo_start; const int32_t* kv_len; const int32_t* qo_offset;
   const int32_t* kv_page_indptr;
+  int32_t* status; int32_t batch;
   int32_t total_q, num_kv_heads, num_qo_heads, kbn, num_pages;
 };
 
@@ -146,7 +147,7 @@ sparse_index_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int32_t*
   const int64_t n = static_cast<int64_t>(a.total_q) * a.num_kv_heads;
   if (gid >= n) return;
   const int kvh = static_cast<int>(gid / a.total_q), t = static_cast<int>(gid % a.total_q);
-  const int b = a.token_batch[t];
+  const int b = chk(a.token_batch[t], 0, a.batch, a.status);
   const int page_base = a.kv_page_indptr[b];
   const int32_t* row = a.kbi + static_cast<int64_t>(t) * a.kbi_stride_tok + static_cast<int64_t>(kvh) * a.kbi_stride_head;
   uint32_t mask = 0;
@@ -180,7 +181,7 @@ sparse_index_smem_kernel(const IndexArgs a, int32_t* __restrict__ bin_count, int
 #pragma unroll
   for (int s = 0; s < KBN; ++s) gpage[s] = -1;
   if (t < a.total_q) {
-    const int b = a.token_batch[t];
+    const int b = chk(a.token_batch[t], 0, a.batch, a.status);
     const int page_base = a.kv_page_indptr[b];
     const int32_t* row = a.kbi + static_cast<int64_t>(t) * a.kbi_stride_tok + static_cast<int64_t>(kvh) * a.kbi_stride_head;
 #pragma unroll
@@ -354,9 +355,9 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   const int4 item = items[item_idx];
   const int NP = p.num_logical_pages;
   const int kvh = item.x / NP, gp = item.x % NP;
-  const int b = p.page_batch[gp];
+  const int b = chk(p.page_batch[gp], 0, p.batch, p.status);
   const int lpage = gp - p.kv_page_indptr[b];
-  const int phys = p.kv_indices[gp];
+  const int phys = chk(p.kv_indices[gp], 0, static_cast<int>(p.kv_extent), p.status);
   const int G = p.num_qo_heads / p.num_kv_heads;
   const int tpc = BM / G;                                  // tokens per chunk
   const int n_ent = item.z - item.y;
@@ -750,7 +751,7 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   IndexArgs ia;
   ia.kbi = p.kv_block_indexes; ia.kbi_stride_tok = p.kbi_stride_tok; ia.kbi_stride_head = p.kbi_stride_head;
   ia.token_batch = p.token_batch; ia.qo_start = p.qo_start; ia.kv_len = p.kv_len; ia.qo_offset = p.qo_offset;
-  ia.kv_page_indptr = p.kv_page_indptr;
+  ia.kv_page_indptr = p.kv_page_indptr; ia.status = p.status; ia.batch = p.batch;
   ia.total_q = p.total_q; ia.num_kv_heads = p.num_kv_heads; ia.num_qo_heads = p.num_qo_heads;
   ia.kbn = p.kv_block_num; ia.num_pages = static_cast<int32_t>(NP);
   const int64_t n_thr = static_cast<int64_t>(p.total_q) * p.num_kv_heads;

@@ -50,9 +50,11 @@ constexpr uint32_t kEmuMask = 0x5252;              // pairs (of 16 per 32 column
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13,
            V_FIX = 15, NUM_BARS = 16 };
 
-struct Knobs {            // per-phase clock trace of one CTA (read only in builds with -DMSA_DEBUG_HOOKS)
-  unsigned long long* trace;   // [4 roles][512 tiles][8 tags] clock64 samples, or null
+struct Knobs {            // read only in builds with -DMSA_DEBUG_HOOKS
+  unsigned long long* trace;   // per-phase clock trace of one CTA: [4 roles][512 tiles][8 tags] clock64 samples, or null
   int trace_cta;
+  int stall_tile;              // >= 0: the producer stops before this K tile and issues nothing after it
+  uint32_t spin_limit;         // > 0: polls a bounded wait makes before it gives up (instead of kSpinLimit)
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -71,8 +73,12 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef MSA_DEBUG_HOOKS
   const bool tracing = kn.trace != nullptr && static_cast<int>(blockIdx.x) == kn.trace_cta;
+  const uint32_t spin_limit = kn.spin_limit ? kn.spin_limit : kSpinLimit;
+  const int stall_tile = kn.stall_tile;
 #else
   constexpr bool tracing = false;                 // the trace calls below compile to nothing
+  constexpr uint32_t spin_limit = kSpinLimit;
+  constexpr int stall_tile = -1;
 #endif
   auto trace = [&](int role, int j, int tag) {
     if (tracing && j < 512) kn.trace[(role * 512 + j) * 8 + tag] = clock64();
@@ -80,7 +86,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
 
   // ---------------- work item ----------------
   const MsaWorkItem w = p.work[blockIdx.x];
-  const int b = w.batch, head = w.head0, row0 = w.row0;
+  const int b = chk(w.batch, 0, p.batch, p.status), head = chk(w.head0, 0, p.num_qo_heads, p.status), row0 = w.row0;
   const int h_r = p.num_qo_heads / p.num_kv_heads;
   const int kvh = head / h_r;
   const int qo_base = p.qo_start[b];
@@ -148,12 +154,13 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     uint32_t fix_phase = 0;
     bool alive = true;
     for (int j = 0; j < n_total && alive; ++j) {
+      if (j == stall_tile) break;                       // test hook: whoever waits for this tile runs out of polls
       const int ks = j % KSTAGES, vs = j % VSTAGES;
-      const int page = paged ? p.kv_indices[page_base + j] : 0;
+      const int page = paged ? chk(p.kv_indices[page_base + j], 0, static_cast<int>(p.kv_extent), p.status) : 0;
       const int valid_rows = min(BN, kv_len - j * BN);
       const bool fix = valid_rows < BN;                 // tail tile: rows past kv_len must read as 0 in V
       if (lane == 0) trace(3, j, 0);
-      alive = mbar_wait(bar(K_EMPTY + ks), ((j / KSTAGES) & 1) ^ 1, abort_flag);
+      alive = mbar_wait(bar(K_EMPTY + ks), ((j / KSTAGES) & 1) ^ 1, abort_flag, spin_limit);
       if (lane == 0) trace(3, j, 1);
       if (!alive) break;
       if (elect_one()) {
@@ -167,7 +174,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       }
       __syncwarp();
       if (!has_o) continue;
-      alive = mbar_wait(bar(V_EMPTY + vs), ((j / VSTAGES) & 1) ^ 1, abort_flag);
+      alive = mbar_wait(bar(V_EMPTY + vs), ((j / VSTAGES) & 1) ^ 1, abort_flag, spin_limit);
       if (lane == 0) trace(3, j, 2);
       if (!alive) break;
       if (elect_one()) {
@@ -182,7 +189,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       }
       __syncwarp();
       if (fix && alive && has_o) {
-        alive = mbar_wait(bar(V_FIX), fix_phase, abort_flag);
+        alive = mbar_wait(bar(V_FIX), fix_phase, abort_flag, spin_limit);
         alive = __all_sync(0xffffffffu, alive);
         fix_phase ^= 1;
         if (alive) {
@@ -225,9 +232,9 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         mma_ts(tmem + 256 + x * kHeadDim, tmem + x * BN + k * 8, dv_hi | ((va + k * (2048 >> 4)) & 0x3FFF), IDESC_PV,
                (j > 0 || k > 0) ? 1u : 0u);
     };
-    bool alive = n_total > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag) : true;
+    bool alive = n_total > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag, spin_limit) : true;
     if (alive && n_total > 0) {
-      alive = mbar_wait(bar(K_FULL + 0), 0, abort_flag);
+      alive = mbar_wait(bar(K_FULL + 0), 0, abort_flag, spin_limit);
       if (alive) {
         tc_fence_after();
         if (elect_one()) {
@@ -247,12 +254,12 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         const bool more = j + 1 < n_tiles[x];
         // the tiles this step reads normally landed long ago: check them before P, and only once per j
         if (x == 0 || j >= n_tiles[0]) {
-          if (has_o) alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag);
+          if (has_o) alive = mbar_wait(bar(V_FULL + j % VSTAGES), (j / VSTAGES) & 1, abort_flag, spin_limit);
           if (alive && j + 1 < n_total)
-            alive = mbar_wait(bar(K_FULL + (j + 1) % KSTAGES), ((j + 1) / KSTAGES) & 1, abort_flag);
+            alive = mbar_wait(bar(K_FULL + (j + 1) % KSTAGES), ((j + 1) / KSTAGES) & 1, abort_flag, spin_limit);
         }
         if (lane == 0) trace(2, j, x * 4 + 1);
-        if (alive) alive = mbar_wait(bar(P_FULL + x), j & 1, abort_flag);
+        if (alive) alive = mbar_wait(bar(P_FULL + x), j & 1, abort_flag, spin_limit);
         if (!alive) break;
         tc_fence_after();
         if (lane == 0) trace(2, j, x * 4 + 2);
@@ -296,7 +303,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
 
     for (int j = 0; j < nx && alive; ++j) {
       if (r == 0) trace(x, j, 0);
-      alive = mbar_wait(bar(S_FULL + x), j & 1, abort_flag);
+      alive = mbar_wait(bar(S_FULL + x), j & 1, abort_flag, spin_limit);
       if (!alive) break;
       tc_fence_after();
       if (r == 0) trace(x, j, 1);
@@ -407,7 +414,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     }
 
     // ---- epilogue ----
-    if (alive && nx > 0 && has_o) alive = mbar_wait(bar(O_FULL + x), 0, abort_flag);
+    if (alive && nx > 0 && has_o) alive = mbar_wait(bar(O_FULL + x), 0, abort_flag, spin_limit);
     if (alive && has_o) {
       tc_fence_after();
       const float vsh = p.v_scale_head ? p.v_scale_head[kvh] : 1.f;
@@ -484,7 +491,7 @@ bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-Knobs g_knobs = {nullptr, 0};
+Knobs g_knobs = {nullptr, 0, -1, 0};
 
 }  // namespace
 
@@ -560,5 +567,12 @@ int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 extern "C" void msa_debug_tc_trace(unsigned long long* buf, int cta) {
   msa::tc::g_knobs.trace = buf;
   msa::tc::g_knobs.trace_cta = cta;
+}
+// Test hook (builds with -DMSA_DEBUG_HOOKS only): make the bounded waits of the dense prefill kernel run out.
+// The TMA producer of every CTA stops before K tile `tile` (-1: never) and issues nothing after it -- no copy
+// is outstanding when the CTA gives up -- and a wait gives up after `spin_limit` polls (0: the normal limit).
+extern "C" void msa_debug_tc_stall(int tile, unsigned spin_limit) {
+  msa::tc::g_knobs.stall_tile = tile;
+  msa::tc::g_knobs.spin_limit = spin_limit;
 }
 #endif

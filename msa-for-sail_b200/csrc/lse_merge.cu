@@ -7,6 +7,7 @@
 // (csrc/include/sm80_fmha_reduction.hpp:133-215); partials here are fp32 or bf16 and the LSE
 // is a natural logarithm.  Half a warp handles one (token, head).
 #include "common.cuh"
+#include "nvtx_range.h"
 
 namespace msa {
 namespace {
@@ -97,6 +98,7 @@ extern "C" int msa_lse_merge_ex(const void* partial_o, int32_t partial_dtype, co
                                 float out_scale, msa_stream_t stream) {
   if (!partial_o || !partial_lse || (!out && !lse_out) || num_splits < 1 || total_q < 0 || num_heads <= 0)
     return MSA_ERR_BAD_ARG;
+  msa::NvtxRange range("msa_lse_merge");
   const int64_t rows = static_cast<int64_t>(total_q) * num_heads;
   if (rows == 0) return MSA_OK;
   const int64_t blocks = (rows + 15) / 16;

@@ -5,6 +5,7 @@
 // tiles per batch item, the split count -- hence the work list has a fixed number of items; a row
 // tile past a sequence's rows and a chunk past its key tiles are empty items.
 #include "common.cuh"
+#include "nvtx_range.h"
 
 namespace msa {
 namespace {
@@ -99,6 +100,7 @@ extern "C" int msa_plan_device(const MsaPlanDeviceArgs* a, msa_stream_t stream) 
   if (a->num_splits < 1 || a->max_total_q < 0 || a->row_tiles < 1) return MSA_ERR_BAD_ARG;
   if (a->token_batch && !a->qo_start) return MSA_ERR_BAD_ARG;
   if (a->batch == 0) return MSA_OK;
+  msa::NvtxRange range("msa_plan_device");
   msa::plan_device_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(*a);
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
 }

@@ -64,7 +64,7 @@ score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
   constexpr int UNROLL = R == 4 ? 8 : 16;        // 16-byte loads in flight per lane
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const MsaWorkItem w = p.work[blockIdx.y];
-  const int b = w.batch, head0 = w.head0;
+  const int b = chk(w.batch, 0, p.batch, p.status), head0 = chk(w.head0, 0, p.num_qo_heads, p.status);
   const int h_r = p.num_qo_heads / p.num_kv_heads;
   const int kvh = head0 / h_r, G = p.pack;
   const int qo_base = p.qo_start[b];
@@ -114,7 +114,7 @@ score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
   const int64_t load_step = static_cast<int64_t>(KPL) * p.k_stride_tok * e;     // bytes between a lane's loads
   const int stride = gridDim.x * NWARPS;
   for (int t = w.kv_tile_begin + blockIdx.x * NWARPS + warp; t < w.kv_tile_end; t += stride) {
-    const int phys = p.kv_indices[page_base + t];
+    const int phys = chk(p.kv_indices[page_base + t], 0, static_cast<int>(p.kv_extent), p.status);
     const unsigned char* kp = kbase + static_cast<int64_t>(phys) * p.k_stride_page * e;
     float mx[R];
 #pragma unroll

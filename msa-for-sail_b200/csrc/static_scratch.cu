@@ -8,6 +8,7 @@
 // points them at a fixed array in device global memory that is part of this module, so the call
 // itself allocates nothing.
 #include "common.cuh"
+#include "nvtx_range.h"
 
 namespace msa {
 int fmha_mma_launch(const MsaFmhaParams& p, cudaStream_t stream);
@@ -60,6 +61,7 @@ extern "C" int msa_fmha_fwd_split_static(const MsaFmhaParams* pp, const int32_t*
   const long long rows = static_cast<long long>(p.num_splits) * p.total_q * p.num_qo_heads;
   if (rows > kMaxRows) return MSA_ERR_TOO_LARGE;
   if (rows == 0) return MSA_OK;
+  msa::NvtxRange range("msa_fmha_fwd_split_static");
 
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return MSA_ERR_LAUNCH;

@@ -50,8 +50,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after kSpinLimit polls or as soon as another thread of the CTA has
 // raised the abort flag; returns false in that case (and raises the flag itself).
 constexpr uint32_t kSpinLimit = 1u << 21;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }

@@ -16,6 +16,7 @@
 // HBM traffic is one read of the valid part of the score tensor plus the index write; no
 // transpose workspace (upstream needs one, api.py:1818-1821).
 #include "common.cuh"
+#include "nvtx_range.h"
 
 namespace msa {
 namespace {
@@ -140,7 +141,81 @@ constexpr int kFilterFold = 16;                  // candidates folded per networ
 constexpr int kFilterWarps = 4;
 constexpr int kFilterBoundPages = 256;           // pages pass A looks at
 
-template <int TOPK, typename T>
+// Keys of the filtering kernel.  64-bit integer compares and selects run on a quarter-rate pipe on sm_100 (the
+// thread-per-row kernel above is bound by it), so the networks here work on 32-bit registers only:
+//   Key2  an (order key, page) pair compared as (key desc, page asc): 3 compares + 4 selects per exchange;
+//   Key1  bf16 scores: the upper half of the order key is exact for them, so (key16 << 16 | ~page16) is one
+//         32-bit word and an exchange is one max and one min.  Not used with forced pages, which rank as the
+//         fp32 maximum -- a score bf16 cannot tell from its own largest finite value.
+struct Key2 {
+  uint32_t o, i;
+  static __device__ __forceinline__ Key2 none() { return {0u, 0xffffffffu}; }            // below every real key
+  static __device__ __forceinline__ Key2 make(float v, int page) { return {ord_key(v), static_cast<uint32_t>(page)}; }
+  __device__ __forceinline__ bool is_none() const { return o == 0u; }
+  __device__ __forceinline__ uint32_t page() const { return i; }
+  __device__ __forceinline__ float score() const { return ord_to_float(o); }
+  static __device__ __forceinline__ void order(Key2& a, Key2& b) {                        // a ranks before b afterwards
+    const bool sw = b.o > a.o || (b.o == a.o && b.i < a.i);
+    const Key2 hi = {sw ? b.o : a.o, sw ? b.i : a.i}, lo = {sw ? a.o : b.o, sw ? a.i : b.i};
+    a = hi; b = lo;
+  }
+  static __device__ __forceinline__ Key2 best(const Key2& a, const Key2& b) {
+    const bool sw = b.o > a.o || (b.o == a.o && b.i < a.i);
+    return {sw ? b.o : a.o, sw ? b.i : a.i};
+  }
+};
+struct Key1 {
+  uint32_t k;
+  static __device__ __forceinline__ Key1 none() { return {0u}; }
+  static __device__ __forceinline__ Key1 make(float v, int page) {
+    return {(ord_key(v) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(page))};
+  }
+  __device__ __forceinline__ bool is_none() const { return k == 0u; }
+  __device__ __forceinline__ uint32_t page() const { return 0xffffu - (k & 0xffffu); }
+  // the score of a bf16-born key: the lower half of the order key is all ones for negative scores, zero otherwise
+  __device__ __forceinline__ float score() const {
+    const uint32_t hi = k & 0xffff0000u;
+    return ord_to_float((hi & 0x80000000u) ? hi : (hi | 0xffffu));
+  }
+  static __device__ __forceinline__ void order(Key1& a, Key1& b) {
+    const uint32_t hi = max(a.k, b.k), lo = min(a.k, b.k);
+    a.k = hi; b.k = lo;
+  }
+  static __device__ __forceinline__ Key1 best(const Key1& a, const Key1& b) { return {max(a.k, b.k)}; }
+};
+
+// descending bitonic sort of N keys / merge of a descending list into the sorted top-N list (static indices)
+template <int N, typename K>
+__device__ __forceinline__ void net_sort_desc(K (&v)[N]) {
+#pragma unroll
+  for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          if ((i & k) == 0) K::order(v[i], v[l]); else K::order(v[l], v[i]);
+        }
+      }
+    }
+  }
+}
+template <int N, typename K>
+__device__ __forceinline__ void net_merge_desc(K (&key)[N], const K (&v)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) key[i] = K::best(key[i], v[N - 1 - i]);     // bitonic now
+#pragma unroll
+  for (int j = N >> 1; j > 0; j >>= 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int l = i ^ j;
+      if (l > i) K::order(key[i], key[l]);
+    }
+  }
+}
+
+template <int TOPK, typename T, typename K>
 __global__ void __launch_bounds__(kFilterWarps * 32, 4)
 topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles,
                    int total_q, int nvp, int force_begin, int force_end_start) {
@@ -161,30 +236,31 @@ topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
     return v;
   };
 
-  TopList<TOPK> top;
-  top.init();
+  K top[TOPK];
+#pragma unroll
+  for (int i = 0; i < TOPK; ++i) top[i] = K::none();
   float thr = __uint_as_float(0x7FFFFFFFu);       // NaN: nothing is rejected while the list is not full
   int cnt = 0;
 
   auto fold16 = [&](int s0) {                     // all lanes: buffered candidates [s0, s0 + 16) -> sorted list
-    u64 c[kFilterFold];
+    K c[kFilterFold];
 #pragma unroll
     for (int s2 = 0; s2 < kFilterFold; ++s2) {
       const int pg = min(static_cast<int>(buf[(s0 + s2) * 32 + lane]), nvp - 1);   // stale slots hold older pages
       const float v = load(pg);
-      c[s2] = s0 + s2 < cnt ? ((static_cast<u64>(ord_key(v)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(pg))) : 0ull;
+      c[s2] = s0 + s2 < cnt ? K::make(v, pg) : K::none();
     }
-    TopList<kFilterFold>::sort_desc(c);
-    u64 blk[TOPK];                                // the best min(TOPK, 16) candidates, zero padded
+    net_sort_desc<kFilterFold, K>(c);
+    K blk[TOPK];                                  // the best min(TOPK, 16) candidates, padded with "none"
 #pragma unroll
-    for (int i = 0; i < TOPK; ++i) blk[i] = i < kFilterFold ? c[i] : 0ull;
-    top.merge_sorted(blk);
+    for (int i = 0; i < TOPK; ++i) blk[i] = i < kFilterFold ? c[i] : K::none();
+    net_merge_desc<TOPK, K>(top, blk);
   };
   auto fold_all = [&]() {
     fold16(0);
     if (__any_sync(0xffffffffu, cnt > kFilterFold)) fold16(kFilterFold);
     cnt = 0;
-    thr = ord_to_float(static_cast<uint32_t>(top.key[TOPK - 1] >> 32));
+    thr = top[TOPK - 1].score();                  // NaN while the list is not full (and if its last entry is a NaN)
   };
 
 #pragma unroll 1
@@ -198,10 +274,18 @@ topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
     float gm[16];
 #pragma unroll
     for (int g = 0; g < 16; ++g) gm[g] = -INFINITY;
-    for (int p0 = 0; p0 < na; p0 += 16) {
+    // two blocks of 16 loads in flight: the second is issued before the first is consumed
+    float cur[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (p0 + u < na) gm[u] = fmaxf(gm[u], load(p0 + u));
+    for (int u = 0; u < 16; ++u) cur[u] = u < na ? load(u) : -INFINITY;
+    for (int p0 = 0; p0 < na; p0 += 16) {
+      float nxt[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) nxt[u] = p0 + 16 + u < na ? load(p0 + 16 + u) : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) gm[u] = fmaxf(gm[u], cur[u]);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
     }
     // TOPK distinct pages must reach the bound: fold the 16 maxima in groups of 16 / TOPK (each group's
     // maximum is one real score) and take the smallest
@@ -235,7 +319,36 @@ topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
     for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
   }
   if (__any_sync(0xffffffffu, cnt > 0)) fold_all();
-  if (t < total_q) emit_ascending<TOPK>(top.key, out + (static_cast<size_t>(t) * num_heads + head) * TOPK);
+  if (t >= total_q) return;
+
+  // page indices ascending, -1 (empty slot; cannot occur when nvp > TOPK) last
+  uint32_t idx[TOPK];
+#pragma unroll
+  for (int i = 0; i < TOPK; ++i) idx[i] = top[i].is_none() ? 0xffffffffu : top[i].page();
+#pragma unroll
+  for (int k = 2; k <= TOPK; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll
+      for (int i = 0; i < TOPK; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const uint32_t a = idx[i], b = idx[l];
+          const bool up = (i & k) == 0;
+          idx[i] = up ? min(a, b) : max(a, b);
+          idx[l] = up ? max(a, b) : min(a, b);
+        }
+      }
+    }
+  }
+  int32_t* dst = out + (static_cast<size_t>(t) * num_heads + head) * TOPK;
+#pragma unroll
+  for (int i = 0; i < TOPK; i += 4) {
+    int4 v;
+    v.x = static_cast<int32_t>(idx[i]); v.y = static_cast<int32_t>(idx[i + 1]);
+    v.z = static_cast<int32_t>(idx[i + 2]); v.w = static_cast<int32_t>(idx[i + 3]);
+    *reinterpret_cast<int4*>(dst + i) = v;                  // 0xffffffff == -1
+  }
 }
 
 template <int TOPK, typename T>
@@ -404,8 +517,11 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
   if (ctas >= 148LL * 8 && nvp <= 65535) {
     const long long fctas = (ctas + kFilterWarps - 1) / kFilterWarps;
     if (fctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
-    topk_filter_kernel<TOPK, T><<<static_cast<unsigned>(fctas), kFilterWarps * 32, 0, stream>>>(scores, out, H, K, T_, nvp,
-                                                                                              fb, fe_start);
+    const unsigned fg = static_cast<unsigned>(fctas);
+    if (sizeof(T) == 2 && fb == 0 && fe == 0)      // bf16 scores, no forced pages: one-word keys
+      topk_filter_kernel<TOPK, T, Key1><<<fg, kFilterWarps * 32, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
+    else
+      topk_filter_kernel<TOPK, T, Key2><<<fg, kFilterWarps * 32, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
     return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
   }
   // enough slices to put ~16 warps on every SM, bounded by the pages there are to scan
@@ -429,6 +545,7 @@ extern "C" int msa_topk_select(const void* scores, int32_t score_dtype, int32_t*
   if (!scores || !out || num_heads < 0 || total_q < 0 || max_k_tiles <= 0) return MSA_ERR_BAD_ARG;
   if (num_valid_pages <= 0 || num_valid_pages > max_k_tiles) return MSA_ERR_BAD_ARG;
   if (force_begin < 0 || force_end < 0 || force_begin + force_end > topk) return MSA_ERR_BAD_ARG;
+  msa::NvtxRange range("msa_topk_select");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 #define MSA_TOPK_CASE(KK)                                                                                          \
   case KK:                                                                                                         \

@@ -2,12 +2,19 @@
 
 There is no fallback: if the shared library is missing or was built for another
 ABI revision, importing this module raises.
+
+``MSA_BOUNDS_CHECK=1`` in the environment loads ``libmsa_b200_check.so`` instead (build it with
+``build.py --bounds-check``): same ABI, every index a kernel reads from a caller's table is
+range-checked and a violation comes back in the status word as ``STATUS_BOUNDS`` (upstream:
+``FMHA_GMEM_CHECK=1``, jit.py:67).
 """
 import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmsa_b200.so")
+BOUNDS_CHECK = os.environ.get("MSA_BOUNDS_CHECK", "0") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "libmsa_b200_check.so" if BOUNDS_CHECK else "libmsa_b200.so")
+STATUS_OK, STATUS_TIMEOUT, STATUS_BOUNDS = 0, 1, 2
 
 MSA_DT_BF16, MSA_DT_E4M3, MSA_DT_F32 = 0, 1, 2
 FLAG_OUT_O, FLAG_OUT_SCORE, FLAG_SPARSE = 1, 2, 4

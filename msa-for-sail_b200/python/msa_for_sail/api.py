@@ -42,7 +42,8 @@ def _status_word(device):
 
 
 def last_status(device=None, reset=True):
-    """Read (synchronously) the device status word: 0 = ok, 1 = a kernel wait timed out."""
+    """Read (synchronously) the device status word: 0 = ok, 1 = a kernel wait timed out, 2 = (bounds-checked
+    build) a kernel found an out-of-range index in one of the caller's tables and clamped it."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     w = _status_word(device)
     v = int(w.item())
@@ -402,6 +403,7 @@ def _fmha_sail_plan(
         "pack_factor": pack,
         "orig_num_qo_heads": orig_num_qo_heads,
         "num_kv_heads": hkv,
+        "kv_heads_given": num_kv_heads != -1,
         "qo_len_uniform": qo_len_uniform,
         "graph_safe": graph_safe,
         "page_size": page_size,
@@ -702,8 +704,13 @@ def _fmha_sail(
             raise ValueError(f"plan allows at most {plan['total_qo_len']} query tokens, q has {nnz_qo}")
     elif plan["total_qo_len"] != nnz_qo:
         raise ValueError(f"plan was made for {plan['total_qo_len']} query tokens, q has {nnz_qo}")
-    if plan["orig_num_qo_heads"] != num_qo_heads or plan["num_kv_heads"] != num_kv_heads:
+    if plan["orig_num_qo_heads"] != num_qo_heads:
         raise ValueError("plan head counts do not match q / k")
+    if plan["num_kv_heads"] != num_kv_heads:
+        # A plan made without num_kv_heads does not pin the KV head count (upstream takes it from K's shape at
+        # run time, api.py:1275-1290): such a plan has one query head per work item, which fits any grouping.
+        if plan.get("kv_heads_given", True) or plan["pack_factor"] != 1 or plan["is_sparse"] or num_qo_heads % num_kv_heads:
+            raise ValueError("plan head counts do not match q / k")
     if plan["is_sparse"] != (kv_block_indexes is not None):
         raise ValueError("plan sparse mode (kv_block_num) does not match kv_block_indexes")
     if (plan_page > 0) != is_paged:

@@ -36,3 +36,21 @@ def test_defaults_and_work_model():
     cfg2 = m.parse_format("--format=seqlen_q:[1],seqlen_k:[4096],num_qo_heads:8,num_kv_heads:1,kv_block_num:4")
     assert cfg2["sparse_mode"] == "Sparse"
     assert m.flops_and_bytes(cfg2)[0] == 8 * 512 * 4 * 128
+
+
+def test_sweep_sections_enumerate_the_upstream_tables():
+    m = _mod()
+    rows = list(m.sweep_cases("prefill", seqs=(8192, 16384), tp=(1, 4)))
+    assert [(c["num_qo_heads"], c["num_kv_heads"], c["seqlen_q"][0]) for _, c, _ in rows] == [
+        (64, 4, 8192), (64, 4, 16384), (16, 1, 8192), (16, 1, 16384)]
+    assert all(not c["is_paged"] and c["sparse_mode"] == "Off" and not mbu for _, c, mbu in rows)
+    rows = list(m.sweep_cases("sparse_decode", decode_k=(8192,), decode_b=(32,), topk=8))
+    assert [c["sparse_mode"] for _, c, _ in rows] == ["Off", "Sparse"] and all(mbu for _, _, mbu in rows)
+    assert rows[1][1]["kv_block_num"] == 8 and rows[1][1]["seqlen_q"] == [8] * 32 and rows[1][1]["selection"] == "first"
+    assert [len(list(m.sweep_cases(s_))) > 0 for s_ in m.SWEEP_SECTIONS] == [True] * 6
+    assert m.TSV_HEADER[:4] == ["q_len", "kv_len", "dtype", "batch_size"] and len(m.TSV_HEADER) == 13 == len(m.TABLE)
+    # a sparse row counts the keys it reads, a dense row the causal triangle
+    sp = rows[1][1]
+    assert m.sweep_work(sp)[0] == 32 * 64 * (8 * 8 * 128) * 256 * 2
+    dn = list(m.sweep_cases("paged_prefill", seqs=(256,)))[0][1]
+    assert m.sweep_work(dn)[0] == 64 * (256 * 256 - 256 * 255 // 2) * 256 * 2
