@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "python", "msa_for_sail", "libmsa_b200.so")
 OUT_CHECK = os.path.join(HERE, "python", "msa_for_sail", "libmsa_b200_check.so")
 CHECK_FLAGS = ["-DMSA_BOUNDS_CHECK", "-DMSA_DEBUG_HOOKS"]
-SOURCES = ["api.cu", "fmha_mma.cu", "fmha_tc.cu", "fmha_sparse_tc.cu", "fmha_sparse_fused.cu", "fmha_decode_tc.cu", "score_gemv.cu", "plan_device.cu", "topk_select.cu", "lse_merge.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "fmha_mma.cu", "fmha_tc.cu", "fmha_sparse_tc.cu", "fmha_decode_tc.cu", "score_gemv.cu", "plan_device.cu", "topk_select.cu", "lse_merge.cu", "static_scratch.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
          "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC,

@@ -1,6 +1,5 @@
 // C ABI front end: argument checks, kernel selection, the host-side dense planner.
 #include <algorithm>
-#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
@@ -17,19 +16,6 @@ int fmha_decode_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int fmha_sparse_tc_supported(const MsaFmhaParams& p);
 int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream);
 int64_t fmha_sparse_tc_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
-int fmha_sparse_fused_launch(const MsaFmhaParams& p, cudaStream_t stream);
-int64_t fmha_sparse_fused_workspace_bytes(int64_t total_q, int num_qo_heads, int num_kv_heads, int kbn, int64_t num_pages);
-
-// Which schedule sparse prefill runs on: "band" = the persistent kernel that merges its partials while they
-// are still in the L2 (fmha_sparse_fused.cu), "page" = attention kernel + separate merge kernel
-// (fmha_sparse_tc.cu).  Read once from MSA_SPARSE_SCHEDULE.
-static bool sparse_schedule_is_band() {
-  static const bool band = [] {
-    const char* e = getenv("MSA_SPARSE_SCHEDULE");
-    return e != nullptr && e[0] == 'b';
-  }();
-  return band;
-}
 }  // namespace msa
 
 namespace msa {
@@ -87,8 +73,7 @@ extern "C" int msa_fmha_fwd(const MsaFmhaParams* pp, msa_stream_t stream_) {
   const MsaFmhaParams& p = *pp;
   if (const int rc = msa::validate_fmha(p, false)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (msa::fmha_sparse_tc_supported(p))
-    return msa::sparse_schedule_is_band() ? msa::fmha_sparse_fused_launch(p, stream) : msa::fmha_sparse_tc_launch(p, stream);
+  if (msa::fmha_sparse_tc_supported(p)) return msa::fmha_sparse_tc_launch(p, stream);
   if (msa::score_gemv_supported(p)) return msa::score_gemv_launch(p, stream);
   if (msa::fmha_decode_tc_supported(p)) return msa::fmha_decode_tc_launch(p, stream);
   if (msa::fmha_tc_supported(p)) return msa::fmha_tc_launch(p, stream);
@@ -172,8 +157,7 @@ extern "C" int64_t msa_sparse_workspace_bytes(int64_t total_q, int32_t num_qo_he
   if (total_q < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads || kv_block_num <= 0 ||
       num_logical_pages < 0)
     return MSA_ERR_BAD_ARG;
-  return std::max(msa::fmha_sparse_tc_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages),
-                  msa::fmha_sparse_fused_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages));
+  return msa::fmha_sparse_tc_workspace_bytes(total_q, num_qo_heads, num_kv_heads, kv_block_num, num_logical_pages);
 }
 
 extern "C" const char* msa_status_string(int code) {

@@ -54,8 +54,13 @@ constexpr int MAX_STAGES = 6;
 constexpr int QUAD_MAX_ROWS = 16;               // rows of a work item the 4-way column split accepts
 constexpr int STAGE_LD = kHeadDim + 4;          // floats per staged O row (padding spreads the banks)
 
+// PV_DONE completes once per tile (a warp that rescales O at tile j waits for P_{j-1} V: at that point the
+// barrier is at most one phase behind, so the parity wait is unambiguous).  The epilogue must NOT wait on it: a
+// softmax warp can finish its last tile while P_{n-2} V is still waiting for its V tile, i.e. two phases ahead
+// of the barrier, where a parity wait for phase n - 1 reads phase n - 3 as "done".  O_DONE completes once, after
+// the last P V.
 enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 7, V_FULL = 13, V_EMPTY = 19, S_FULL = 25, P_FULL = 27, PV_DONE = 29,
-           V_FIX = 30, NUM_BARS = 31 };
+           V_FIX = 30, O_DONE = 31, NUM_BARS = 32 };
 
 #ifdef MSA_DEBUG_HOOKS
 // diagnostic timeline: when set, every CTA records 16 words (see msa_debug_decode_trace)
@@ -191,6 +196,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     }
     for (int s = 0; s < NBUF; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 32 * n_active_warps); }
     mbar_init(bar(PV_DONE), 1);
+    mbar_init(bar(O_DONE), 1);
     mbar_init(bar(V_FIX), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -379,7 +385,10 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         if (alive) alive = mbar_wait(bar(P_FULL + j % NBUF), (j / NBUF) & 1, abort_flag);
         if (!alive) break;
         tc_fence_after();
-        if (elect_one()) { issue_pv(j); mma_commit(bar(V_EMPTY + j % STAGES)); mma_commit(bar(PV_DONE)); }
+        if (elect_one()) {
+          issue_pv(j); mma_commit(bar(V_EMPTY + j % STAGES)); mma_commit(bar(PV_DONE));
+          if (j == n_tiles - 1) mma_commit(bar(O_DONE));
+        }
         __syncwarp();
       }
       if (NBUF == 1 && j + 1 < n_tiles) { next_qk(j, alive); if (!alive) break; }
@@ -641,7 +650,7 @@ decode_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     }
 
     // ---- epilogue ----
-    if (alive && n_tiles > 0 && has_o) alive = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, abort_flag);
+    if (alive && n_tiles > 0 && has_o) alive = mbar_wait(bar(O_DONE), 0, abort_flag);
     if (trace) trace[9] = clock64() - clk0;
     if constexpr (QUAD) {
       // every MMA and every TMA load of this CTA has completed: the K ring is free to stage the

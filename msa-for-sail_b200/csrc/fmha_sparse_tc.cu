@@ -292,23 +292,26 @@ sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restric
     mx = fmaxf(mx, lse[s]);
   }
   const float mxs = (mx == -INFINITY) ? 0.f : mx;
-  float acc[8];
+  // two columns per packed FMA; a bf16 pair widens with one shift and one mask
+  uint64_t acc2[4];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  for (int c = 0; c < 4; ++c) acc2[c] = f2_pack(0.f, 0.f);
   float sw = 0.f;
 #pragma unroll
   for (int s = 0; s < KBN; ++s) {
     const float w = lse[s] != -INFINITY ? __expf(lse[s] - mxs) : 0.f;
     if (w != 0.f) {                                          // value select after an unconditional load
       sw += w;
+      const uint64_t w2 = f2_pack(w, w);
       const uint32_t* r4 = reinterpret_cast<const uint32_t*>(&raw[s]);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        acc[2 * c] = fmaf(w, bf16_bits_to_float(r4[c] & 0xffff), acc[2 * c]);
-        acc[2 * c + 1] = fmaf(w, bf16_bits_to_float(r4[c] >> 16), acc[2 * c + 1]);
-      }
+      for (int c = 0; c < 4; ++c)
+        acc2[c] = f2_fma(f2_pack(__uint_as_float(r4[c] << 16), __uint_as_float(r4[c] & 0xffff0000u)), w2, acc2[c]);
     }
   }
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) f2_unpack(acc2[c], acc[2 * c], acc[2 * c + 1]);
   const float sc = sw > 0.f ? out_scale / sw : 0.f;
   __nv_bfloat16* dst = out + static_cast<int64_t>(t) * out_stride_tok + static_cast<int64_t>(h) * out_stride_head + l16 * 8;
   uint4 pk;

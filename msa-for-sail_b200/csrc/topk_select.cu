@@ -9,10 +9,9 @@
 //
 // Layout of the work: a CTA owns 32 consecutive tokens of one head; its lanes read 32
 // consecutive tokens (one coalesced 128-byte line per page row for fp32), its SL warps scan
-// interleaved blocks of TOPK pages.  Each thread keeps its TOPK best 64-bit keys
-// (ord << 32 | ~page) sorted in registers and folds in TOPK new keys at a time with bitonic
-// compare-exchange networks (branch-free: rows of a warp never diverge).  The SL partial lists
-// are merged through shared memory with the same network.
+// interleaved blocks of TOPK pages.  Each thread keeps its TOPK best keys sorted in registers and
+// folds in TOPK new keys at a time with bitonic compare-exchange networks (branch-free: rows of a
+// warp never diverge).  The SL partial lists are merged through shared memory with the same network.
 // HBM traffic is one read of the valid part of the score tensor plus the index write; no
 // transpose workspace (upstream needs one, api.py:1818-1821).
 #include "common.cuh"
@@ -32,128 +31,21 @@ __device__ __forceinline__ uint32_t ord_key(float v) {
   const uint32_t key = bits ^ (static_cast<uint32_t>(static_cast<int32_t>(bits) >> 31) | 0x80000000u);
   return v != v ? 0xFFFFFFFFu : key;
 }
-// the score a key stands for (key 0, "no entry", and the NaN key both map to a NaN)
-__device__ __forceinline__ float ord_to_float(uint32_t key) {
-  return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
-}
 
-using u64 = unsigned long long;
-
-__device__ __forceinline__ void ce_desc(u64& a, u64& b) {      // a >= b afterwards
-  const u64 hi = a > b ? a : b, lo = a > b ? b : a;
-  a = hi; b = lo;
-}
-
-// Sorted (descending) list of the TOPK best keys seen so far, updated TOPK keys at a time with
-// fixed compare-exchange networks: no data-dependent branch, so the 32 rows a warp owns never
-// diverge.  Keys are unique (page index in the low word), hence no tie handling.
-template <int TOPK>
-struct TopList {
-  u64 key[TOPK];
-  __device__ __forceinline__ void init() {
-#pragma unroll
-    for (int i = 0; i < TOPK; ++i) key[i] = 0ull;               // below every real key
-  }
-  // bitonic sort of a block, descending
-  static __device__ __forceinline__ void sort_desc(u64 (&v)[TOPK]) {
-#pragma unroll
-    for (int k = 2; k <= TOPK; k <<= 1) {
-#pragma unroll
-      for (int j = k >> 1; j > 0; j >>= 1) {
-#pragma unroll
-        for (int i = 0; i < TOPK; ++i) {
-          const int l = i ^ j;
-          if (l > i) {
-            if ((i & k) == 0) ce_desc(v[i], v[l]); else ce_desc(v[l], v[i]);
-          }
-        }
-      }
-    }
-  }
-  // merge another descending list: keep the TOPK largest of the 2*TOPK keys, sorted
-  __device__ __forceinline__ void merge_sorted(const u64 (&v)[TOPK]) {
-#pragma unroll
-    for (int i = 0; i < TOPK; ++i) key[i] = key[i] > v[TOPK - 1 - i] ? key[i] : v[TOPK - 1 - i];   // bitonic now
-#pragma unroll
-    for (int j = TOPK >> 1; j > 0; j >>= 1) {
-#pragma unroll
-      for (int i = 0; i < TOPK; ++i) {
-        const int l = i ^ j;
-        if (l > i) ce_desc(key[i], key[l]);
-      }
-    }
-  }
-};
-
-// Page indices of a finished list, ascending, -1 (empty slot; cannot occur when nvp > TOPK) last.
-template <int TOPK>
-__device__ __forceinline__ void emit_ascending(const u64 (&key)[TOPK], int32_t* __restrict__ dst) {
-  uint32_t idx[TOPK];
-#pragma unroll
-  for (int i = 0; i < TOPK; ++i) idx[i] = key[i] == 0ull ? 0xffffffffu : ~static_cast<uint32_t>(key[i]);
-  // ascending bitonic sort of the indices (static register indices)
-#pragma unroll
-  for (int k = 2; k <= TOPK; k <<= 1) {
-#pragma unroll
-    for (int j = k >> 1; j > 0; j >>= 1) {
-#pragma unroll
-      for (int i = 0; i < TOPK; ++i) {
-        const int l = i ^ j;
-        if (l > i) {
-          const uint32_t a = idx[i], b = idx[l];
-          const bool up = (i & k) == 0;
-          idx[i] = up ? min(a, b) : max(a, b);
-          idx[l] = up ? max(a, b) : min(a, b);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < TOPK; i += 4) {
-    int4 v;
-    v.x = static_cast<int32_t>(idx[i]); v.y = static_cast<int32_t>(idx[i + 1]);
-    v.z = static_cast<int32_t>(idx[i + 2]); v.w = static_cast<int32_t>(idx[i + 3]);
-    *reinterpret_cast<int4*>(dst + i) = v;                  // 0xffffffff == -1
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// Prefill-sized inputs: filter first, sort only what survives.
-//
-// A warp owns 32 consecutive tokens (lane = token: every page row is one coalesced line).
-//   pass A: 16 running maxima over the pages p % 16 == g of the first 256 pages; their minimum thr0 is
-//           a lower bound of the TOPK-th best score (16 distinct pages reach it), so a score below it
-//           is out (TOPK 8 / 4 fold the maxima pairwise first; TOPK 32 skips the pass);
-//   pass B: a page is a candidate iff !(v < thr0) && !(v <= thr), thr = the score of the list's last
-//           entry (NaN while the list is not full: everything passes).  Both tests are single float
-//           compares, exact with respect to the key order: an equal score loses to the earlier page
-//           that is already in the list, -0.0 == +0.0, and NaN (which ranks first) passes both.
-//           Candidates are appended to a per-lane buffer of page numbers in shared memory; when any
-//           lane of the warp holds more than 16, all lanes fold theirs into their sorted list with
-//           fixed compare-exchange networks on the exact 64-bit keys, and thr is refreshed.
-// Pass B re-reads what pass A read (from L2: a warp's 256 x 128 bytes were fetched microseconds before);
-// its loads run one block of 16 pages ahead of the compares.  On the shape this is sized for (256 pages,
-// top 16) some 35 of the 256 scores of a row are ever sorted; the rest cost a load and two compares.
-// No shared-memory staging of the scores, so 16 warps per SM hide the latencies; no workspace.
-// ------------------------------------------------------------------------------------------------
-constexpr int kFilterSlots = 32;                 // candidate slots per lane
-constexpr int kFilterFold = 16;                  // candidates folded per network pass
-constexpr int kFilterWarps = 4;
-constexpr int kFilterBoundPages = 256;           // pages pass A looks at
-
-// Keys of the filtering kernel.  64-bit integer compares and selects run on a quarter-rate pipe on sm_100 (the
-// thread-per-row kernel above is bound by it), so the networks here work on 32-bit registers only:
+// Keys of the thread-per-row kernel.  64-bit integer compares and selects run on a quarter-rate pipe on
+// sm_100 (a version of this kernel on (order key << 32 | ~page) words spent 65 % of its time there), so the
+// compare-exchange networks work on 32-bit registers only:
 //   Key2  an (order key, page) pair compared as (key desc, page asc): 3 compares + 4 selects per exchange;
 //   Key1  bf16 scores: the upper half of the order key is exact for them, so (key16 << 16 | ~page16) is one
 //         32-bit word and an exchange is one max and one min.  Not used with forced pages, which rank as the
-//         fp32 maximum -- a score bf16 cannot tell from its own largest finite value.
+//         fp32 maximum -- a score bf16 cannot tell from its own largest finite value -- nor beyond 65 535 pages.
+// Keys are unique (the page is part of them), hence a strict total order: no tie handling anywhere.
 struct Key2 {
   uint32_t o, i;
   static __device__ __forceinline__ Key2 none() { return {0u, 0xffffffffu}; }            // below every real key
-  static __device__ __forceinline__ Key2 make(float v, int page) { return {ord_key(v), static_cast<uint32_t>(page)}; }
+  static __device__ __forceinline__ Key2 make(uint32_t ord, int page) { return {ord, static_cast<uint32_t>(page)}; }
   __device__ __forceinline__ bool is_none() const { return o == 0u; }
   __device__ __forceinline__ uint32_t page() const { return i; }
-  __device__ __forceinline__ float score() const { return ord_to_float(o); }
   static __device__ __forceinline__ void order(Key2& a, Key2& b) {                        // a ranks before b afterwards
     const bool sw = b.o > a.o || (b.o == a.o && b.i < a.i);
     const Key2 hi = {sw ? b.o : a.o, sw ? b.i : a.i}, lo = {sw ? a.o : b.o, sw ? a.i : b.i};
@@ -167,16 +59,11 @@ struct Key2 {
 struct Key1 {
   uint32_t k;
   static __device__ __forceinline__ Key1 none() { return {0u}; }
-  static __device__ __forceinline__ Key1 make(float v, int page) {
-    return {(ord_key(v) & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(page))};
+  static __device__ __forceinline__ Key1 make(uint32_t ord, int page) {
+    return {(ord & 0xffff0000u) | (0xffffu - static_cast<uint32_t>(page))};
   }
   __device__ __forceinline__ bool is_none() const { return k == 0u; }
   __device__ __forceinline__ uint32_t page() const { return 0xffffu - (k & 0xffffu); }
-  // the score of a bf16-born key: the lower half of the order key is all ones for negative scores, zero otherwise
-  __device__ __forceinline__ float score() const {
-    const uint32_t hi = k & 0xffff0000u;
-    return ord_to_float((hi & 0x80000000u) ? hi : (hi | 0xffffu));
-  }
   static __device__ __forceinline__ void order(Key1& a, Key1& b) {
     const uint32_t hi = max(a.k, b.k), lo = min(a.k, b.k);
     a.k = hi; b.k = lo;
@@ -184,7 +71,8 @@ struct Key1 {
   static __device__ __forceinline__ Key1 best(const Key1& a, const Key1& b) { return {max(a.k, b.k)}; }
 };
 
-// descending bitonic sort of N keys / merge of a descending list into the sorted top-N list (static indices)
+// descending bitonic sort of N keys / merge of a descending list into the sorted top-N list (static
+// register indices, no data-dependent branch: the 32 rows a warp owns never diverge)
 template <int N, typename K>
 __device__ __forceinline__ void net_sort_desc(K (&v)[N]) {
 #pragma unroll
@@ -216,112 +104,56 @@ __device__ __forceinline__ void net_merge_desc(K (&key)[N], const K (&v)[N]) {
 }
 
 template <int TOPK, typename T, typename K>
-__global__ void __launch_bounds__(kFilterWarps * 32, 4)
-topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles,
-                   int total_q, int nvp, int force_begin, int force_end_start) {
-  __shared__ uint16_t s_buf[kFilterWarps][kFilterSlots * 32];                    // [slot][lane]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint16_t* buf = s_buf[warp];
+__global__ void __launch_bounds__(256)
+topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles,
+                   int total_q, int nvp, int force_begin, int force_end_start, int slices) {
+  extern __shared__ __align__(8) unsigned char s_raw[];
+  K* s_keys = reinterpret_cast<K*>(s_raw);          // [slices][32][TOPK]
+  const int lane = threadIdx.x & 31, sl = threadIdx.x >> 5;
   const int tok_blocks = (total_q + 31) / 32;
-  const long long wid = static_cast<long long>(blockIdx.x) * kFilterWarps + warp;
-  if (wid >= static_cast<long long>(tok_blocks) * num_heads) return;            // warp-uniform; warps share nothing
-  const int head = static_cast<int>(wid / tok_blocks);
-  const int t = static_cast<int>(wid % tok_blocks) * 32 + lane;
-  // a lane past the last token reads the last token's column and stores nothing
-  const T* col = scores + static_cast<size_t>(head) * max_k_tiles * total_q + min(t, total_q - 1);
-  const bool any_forced = force_begin > 0 || force_end_start < nvp;
-  auto load = [&](int page) -> float {
-    float v = static_cast<float>(col[static_cast<size_t>(page) * total_q]);
-    if (any_forced && (page < force_begin || page >= force_end_start)) v = 3.402823466e+38f;   // ranks as FLT_MAX
-    return v;
-  };
+  const int head = blockIdx.x / tok_blocks;
+  const int t = (blockIdx.x % tok_blocks) * 32 + lane;
+  const bool live = t < total_q;
 
   K top[TOPK];
 #pragma unroll
   for (int i = 0; i < TOPK; ++i) top[i] = K::none();
-  float thr = __uint_as_float(0x7FFFFFFFu);       // NaN: nothing is rejected while the list is not full
-  int cnt = 0;
-
-  auto fold16 = [&](int s0) {                     // all lanes: buffered candidates [s0, s0 + 16) -> sorted list
-    K c[kFilterFold];
+  if (live) {
+    const T* base = scores + static_cast<size_t>(head) * max_k_tiles * total_q + t;
+    // slice sl scans page blocks sl, sl + slices, ... of TOPK consecutive pages each
+    for (int k0 = sl * TOPK; k0 < nvp; k0 += slices * TOPK) {
+      float v[TOPK];
 #pragma unroll
-    for (int s2 = 0; s2 < kFilterFold; ++s2) {
-      const int pg = min(static_cast<int>(buf[(s0 + s2) * 32 + lane]), nvp - 1);   // stale slots hold older pages
-      const float v = load(pg);
-      c[s2] = s0 + s2 < cnt ? K::make(v, pg) : K::none();
-    }
-    net_sort_desc<kFilterFold, K>(c);
-    K blk[TOPK];                                  // the best min(TOPK, 16) candidates, padded with "none"
+      for (int u = 0; u < TOPK; ++u)
+        v[u] = (k0 + u < nvp) ? static_cast<float>(base[static_cast<size_t>(k0 + u) * total_q]) : 0.f;
+      K blk[TOPK];
 #pragma unroll
-    for (int i = 0; i < TOPK; ++i) blk[i] = i < kFilterFold ? c[i] : K::none();
-    net_merge_desc<TOPK, K>(top, blk);
-  };
-  auto fold_all = [&]() {
-    fold16(0);
-    if (__any_sync(0xffffffffu, cnt > kFilterFold)) fold16(kFilterFold);
-    cnt = 0;
-    thr = top[TOPK - 1].score();                  // NaN while the list is not full (and if its last entry is a NaN)
-  };
-
-#pragma unroll 1
-  for (int i = lane; i < kFilterSlots * 32; i += 32) buf[i] = 0;
-  __syncwarp();
-
-  // ---- pass A: a lower bound of the TOPK-th best from 16 interleaved group maxima ----
-  float thr0 = -INFINITY;
-  if (TOPK <= 16 && nvp >= 2 * TOPK) {
-    const int na = min(nvp, kFilterBoundPages);
-    float gm[16];
-#pragma unroll
-    for (int g = 0; g < 16; ++g) gm[g] = -INFINITY;
-    // two blocks of 16 loads in flight: the second is issued before the first is consumed
-    float cur[16];
-#pragma unroll
-    for (int u = 0; u < 16; ++u) cur[u] = u < na ? load(u) : -INFINITY;
-    for (int p0 = 0; p0 < na; p0 += 16) {
-      float nxt[16];
-#pragma unroll
-      for (int u = 0; u < 16; ++u) nxt[u] = p0 + 16 + u < na ? load(p0 + 16 + u) : -INFINITY;
-#pragma unroll
-      for (int u = 0; u < 16; ++u) gm[u] = fmaxf(gm[u], cur[u]);
-#pragma unroll
-      for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
-    }
-    // TOPK distinct pages must reach the bound: fold the 16 maxima in groups of 16 / TOPK (each group's
-    // maximum is one real score) and take the smallest
-    constexpr int STEP = TOPK <= 16 ? 16 / TOPK : 1;
-    thr0 = INFINITY;
-#pragma unroll
-    for (int g = 0; g < 16; g += STEP) {
-      float m = gm[g];
-#pragma unroll
-      for (int e2 = 1; e2 < STEP; ++e2) m = fmaxf(m, gm[g + e2]);
-      thr0 = fminf(thr0, m);
+      for (int u = 0; u < TOPK; ++u) {
+        const int kk = k0 + u;
+        const bool forced = kk < force_begin || kk >= force_end_start;
+        blk[u] = kk < nvp ? K::make(forced ? kForcedOrd : ord_key(v[u]), kk) : K::none();
+      }
+      net_sort_desc<TOPK, K>(blk);
+      net_merge_desc<TOPK, K>(top, blk);
     }
   }
-
-  // ---- pass B: filter, buffer, fold; the loads of block p0 + 16 are in flight while block p0 is compared ----
-  float cur[16];
+  if (slices > 1) {
+    K* mine = s_keys + (static_cast<size_t>(sl) * 32 + lane) * TOPK;
 #pragma unroll
-  for (int u = 0; u < 16; ++u) cur[u] = u < nvp ? load(u) : 0.f;
-  for (int p0 = 0; p0 < nvp; p0 += 16) {
-    float nxt[16];
+    for (int i = 0; i < TOPK; ++i) mine[i] = top[i];
+    __syncthreads();
+    if (sl != 0) return;
+    for (int s2 = 1; s2 < slices; ++s2) {
+      const K* other = s_keys + (static_cast<size_t>(s2) * 32 + lane) * TOPK;
+      K o[TOPK];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) nxt[u] = p0 + 16 + u < nvp ? load(p0 + 16 + u) : 0.f;
-#pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      const float v = cur[u];
-      const bool cand = p0 + u < nvp && !(v < thr0) && !(v <= thr);
-      if (cand) { buf[cnt * 32 + lane] = static_cast<uint16_t>(p0 + u); ++cnt; }
+      for (int i = 0; i < TOPK; ++i) o[i] = other[i];
+      net_merge_desc<TOPK, K>(top, o);
     }
-    if (__any_sync(0xffffffffu, cnt > kFilterFold)) fold_all();
-#pragma unroll
-    for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
   }
-  if (__any_sync(0xffffffffu, cnt > 0)) fold_all();
-  if (t >= total_q) return;
+  if (!live) return;
 
-  // page indices ascending, -1 (empty slot; cannot occur when nvp > TOPK) last
+  // page indices ascending; empty slots (cannot occur when nvp > TOPK) become -1 and sort last
   uint32_t idx[TOPK];
 #pragma unroll
   for (int i = 0; i < TOPK; ++i) idx[i] = top[i].is_none() ? 0xffffffffu : top[i].page();
@@ -349,58 +181,6 @@ topk_filter_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int 
     v.z = static_cast<int32_t>(idx[i + 2]); v.w = static_cast<int32_t>(idx[i + 3]);
     *reinterpret_cast<int4*>(dst + i) = v;                  // 0xffffffff == -1
   }
-}
-
-template <int TOPK, typename T>
-__global__ void __launch_bounds__(256)
-topk_select_kernel(const T* __restrict__ scores, int32_t* __restrict__ out, int num_heads, int max_k_tiles,
-                   int total_q, int nvp, int force_begin, int force_end_start, int slices) {
-  extern __shared__ u64 s_keys[];   // [slices][32][TOPK]
-  const int lane = threadIdx.x & 31, sl = threadIdx.x >> 5;
-  const int tok_blocks = (total_q + 31) / 32;
-  const int head = blockIdx.x / tok_blocks;
-  const int t = (blockIdx.x % tok_blocks) * 32 + lane;
-  const bool live = t < total_q;
-
-  TopList<TOPK> top;
-  top.init();
-  if (live) {
-    const T* base = scores + static_cast<size_t>(head) * max_k_tiles * total_q + t;
-    // slice sl scans page blocks sl, sl + slices, ... of TOPK consecutive pages each
-    for (int k0 = sl * TOPK; k0 < nvp; k0 += slices * TOPK) {
-      float v[TOPK];
-#pragma unroll
-      for (int u = 0; u < TOPK; ++u)
-        v[u] = (k0 + u < nvp) ? static_cast<float>(base[static_cast<size_t>(k0 + u) * total_q]) : 0.f;
-      u64 blk[TOPK];
-#pragma unroll
-      for (int u = 0; u < TOPK; ++u) {
-        const int kk = k0 + u;
-        const bool forced = kk < force_begin || kk >= force_end_start;
-        const uint32_t o = forced ? kForcedOrd : ord_key(v[u]);
-        blk[u] = kk < nvp ? ((static_cast<u64>(o) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(kk))) : 0ull;
-      }
-      TopList<TOPK>::sort_desc(blk);
-      top.merge_sorted(blk);
-    }
-  }
-  if (slices > 1) {
-    u64* mine = s_keys + (static_cast<size_t>(sl) * 32 + lane) * TOPK;
-#pragma unroll
-    for (int i = 0; i < TOPK; ++i) mine[i] = top.key[i];
-    __syncthreads();
-    if (sl != 0) return;
-    for (int s2 = 1; s2 < slices; ++s2) {
-      const u64* other = s_keys + (static_cast<size_t>(s2) * 32 + lane) * TOPK;
-      u64 o[TOPK];
-#pragma unroll
-      for (int i = 0; i < TOPK; ++i) o[i] = other[i];
-      top.merge_sorted(o);
-    }
-  }
-  if (!live) return;
-
-  emit_ascending<TOPK>(top.key, out + (static_cast<size_t>(t) * num_heads + head) * TOPK);
 }
 
 // Few rows (decode): one CTA per (token, head) row, its 256 threads share the row's pages, NK
@@ -512,26 +292,22 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
   }
   const int tok_blocks = (T_ + 31) / 32;
   const long long ctas = static_cast<long long>(tok_blocks) * H;
-  // enough token blocks to give every SM several warps, page numbers that fit the 16-bit candidate
-  // buffer: the filtering kernel
-  if (ctas >= 148LL * 8 && nvp <= 65535) {
-    const long long fctas = (ctas + kFilterWarps - 1) / kFilterWarps;
-    if (fctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
-    const unsigned fg = static_cast<unsigned>(fctas);
-    if (sizeof(T) == 2 && fb == 0 && fe == 0)      // bf16 scores, no forced pages: one-word keys
-      topk_filter_kernel<TOPK, T, Key1><<<fg, kFilterWarps * 32, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
-    else
-      topk_filter_kernel<TOPK, T, Key2><<<fg, kFilterWarps * 32, 0, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start);
-    return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
-  }
   // enough slices to put ~16 warps on every SM, bounded by the pages there are to scan
   int slices = 1;
   while (slices < 8 && ctas * slices < 148LL * 16 && nvp / (slices * 2) >= 2 * TOPK) slices *= 2;
   if (ctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
-  const size_t smem = slices > 1 ? static_cast<size_t>(slices) * 32 * TOPK * sizeof(unsigned long long) : 0;
-  auto kern = topk_select_kernel<TOPK, T>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  kern<<<static_cast<unsigned>(ctas), 32 * slices, smem, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start, slices);
+  const bool one_word = sizeof(T) == 2 && fb == 0 && fe == 0 && nvp <= 65535;      // bf16 scores, nothing forced
+  const size_t smem = slices > 1 ? static_cast<size_t>(slices) * 32 * TOPK * (one_word ? sizeof(Key1) : sizeof(Key2)) : 0;
+  const unsigned grid = static_cast<unsigned>(ctas);
+  if (one_word) {
+    auto kern = topk_select_kernel<TOPK, T, Key1>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, 32 * slices, smem, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start, slices);
+  } else {
+    auto kern = topk_select_kernel<TOPK, T, Key2>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, 32 * slices, smem, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start, slices);
+  }
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
 }
 

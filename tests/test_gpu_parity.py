@@ -129,10 +129,10 @@ def test_topk_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
     (2, 128, 19012, 100, 4, 1, 0, torch.bfloat16),     # top-4
     (1, 1280, 38000, 1100, 16, 0, 0, torch.bfloat16),  # long rows
 ])
-def test_topk_filter_kernel_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
-    """Inputs with at least 1 184 blocks of 32 tokens take the filtering kernel (a warp per 32 tokens,
-    candidates above a running threshold only): quantised scores (ties everywhere), a causal -inf
-    tail per token, signed zeros and NaNs sprinkled in."""
+def test_topk_large_inputs_match_oracle(H, K, T, nvp, topk, fb, fe, dt):
+    """Prefill-sized inputs (tens of thousands of tokens; fp32 scores on two-register keys, bf16 scores without
+    forced pages on one-word keys): quantised scores (ties everywhere), a causal -inf tail per token, signed
+    zeros and NaNs sprinkled in."""
     api = _api()
     g = gen(7 * H + K + T)
     m = torch.randn(H, K, T, generator=g)
@@ -148,9 +148,9 @@ def test_topk_filter_kernel_matches_oracle(H, K, T, nvp, topk, fb, fe, dt):
     assert torch.equal(got.cpu(), ref)
 
 
-def test_topk_filter_kernel_golden_distributions_bitexact():
+def test_topk_large_inputs_golden_distributions_bitexact():
     """The upstream tie distributions (and the signed-zero / NaN ones), repeated along the token axis
-    until the input is large enough for the filtering kernel."""
+    to a prefill-sized input."""
     api = _api()
     z = load_golden("topk_dist.npz")
     for kind in sorted(k[:-3] for k in z.files if k.endswith("_in")):
