@@ -1,8 +1,11 @@
 // Dense causal FMHA forward on the 5th-generation tensor cores (tcgen05 + TMEM) for sm_100a.
 //
 // Serves the prefill shapes of `fmha_sail` (upstream dense/paged mainloop,
-// csrc/include/sm80_fmha_fwd_mainloop.hpp:262-636): bf16 Q/K/V, head_dim 128, ragged K/V or
-// pages of 128 keys, one query head per row tile, optional per-tile max-score and LSE output.
+// csrc/include/sm80_fmha_fwd_mainloop.hpp:262-636): Q/K/V all bf16 or all e4m3, head_dim 128,
+// ragged K/V or pages of 128 keys, one query head per row tile, optional per-tile max-score and
+// LSE output.  With e4m3 operands both products run as kind::f8f6f4 MMAs and P is rounded to
+// e4m3 (upstream feeds e4m3 to the MMA unit only in its score-only pass, same file :62-64, and
+// converts the cache to bf16 otherwise).
 //
 // One CTA = 256 consecutive query rows of one (batch item, head) = two 128-row Q tiles "A" and
 // "B" that walk the same KV tiles, so every K/V tile in shared memory feeds two MMAs and the
@@ -19,8 +22,9 @@
 //               registers to the softmax warpgroups: 224 / 224 / 56 per thread)
 //
 // TMEM (512 columns): S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P aliases the
-// first 64 columns of its S.  Shared memory: Q 64 KB, K 2x32 KB, V 2x32 KB, all in the
-// 128-byte-swizzled layout that both TMA and the UMMA descriptors understand.
+// first 64 columns of its S (32 in e4m3).  Shared memory: Q 64 KB, K 2x32 KB, V 2x32 KB (e4m3:
+// Q 32 KB, K 4x16 KB, V 4x16 KB), all in the 128-byte-swizzled layout that both TMA and the UMMA
+// descriptors understand.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, reports
 // MSA_STATUS_TIMEOUT in the status word, releases its TMEM and exits.
@@ -34,21 +38,37 @@ namespace {
 
 constexpr int BM = 128;                 // rows per Q tile
 constexpr int BN = 128;                 // keys per KV tile
-constexpr int SUB_BYTES = BM * 64 * 2;  // one [128 rows][64 bf16] swizzled sub-tile
-constexpr int TILE_BYTES = 2 * SUB_BYTES;
-constexpr int KSTAGES = 2, VSTAGES = 2;
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
-constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
-constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // + alignment slack
+constexpr int SUB_BYTES = BM * 128;     // one [128 rows][128 bytes] swizzled sub-tile: 64 bf16 or 128 e4m3 per row
 constexpr int NTHREADS = 384;
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
-constexpr float kRescaleThreshold = 8.0f;          // log2 units: P stays <= 2^8
 constexpr uint32_t kEmuMask = 0x5252;              // pairs (of 16 per 32 columns) whose exp2 is computed on the FMA pipe
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13,
-           V_FIX = 15, NUM_BARS = 16 };
+// F8: Q, K, V (and P) are e4m3 and the MMAs are kind::f8f6f4; otherwise bf16 and kind::f16.  A tile is
+// half as large in e4m3, so the K and V rings are twice as deep in the same shared memory.
+template <bool F8>
+struct Cfg {
+  static constexpr int NSUB = F8 ? 1 : 2;                  // sub-tiles per [128][head_dim] tile
+  static constexpr int SUB_ELEMS = F8 ? 128 : 64;          // elements of head_dim per sub-tile
+  static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
+  static constexpr int STAGES = F8 ? 4 : 2;                // depth of the K ring and of the V ring
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_V + STAGES * TILE_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + alignment slack
+  // log2 units.  P = 2^(s - m + offset) stays below 2^(threshold + offset): 2^8 in both formats, and in
+  // e4m3 the offset keeps the small probabilities out of the subnormal range.
+  static constexpr float kRescaleThreshold = F8 ? 4.0f : 8.0f;
+  static constexpr float kPOffset = F8 ? 4.0f : 0.0f;
+};
+
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 5, V_FULL = 9, V_EMPTY = 13, S_FULL = 17, P_FULL = 19, O_FULL = 21,
+           V_FIX = 23, NUM_BARS = 24 };
+
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t x) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(x), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
 
 struct Knobs {            // read only in builds with -DMSA_DEBUG_HOOKS
   unsigned long long* trace;   // per-phase clock trace of one CTA: [4 roles][512 tiles][8 tags] clock64 samples, or null
@@ -57,10 +77,16 @@ struct Knobs {            // read only in builds with -DMSA_DEBUG_HOOKS
   uint32_t spin_limit;         // > 0: polls a bounded wait makes before it gives up (instead of kSpinLimit)
 };
 
+template <bool F8>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                const Knobs kn) {
+  using C = Cfg<F8>;
+  constexpr int TILE_BYTES = C::TILE_BYTES, NSUB = C::NSUB, SUB_ELEMS = C::SUB_ELEMS;
+  constexpr int KSTAGES = C::STAGES, VSTAGES = C::STAGES;
+  constexpr int OFF_Q = C::OFF_Q, OFF_K = C::OFF_K, OFF_V = C::OFF_V, OFF_BAR = C::OFF_BAR;
+  constexpr float kRescaleThreshold = C::kRescaleThreshold, kPOffset = C::kPOffset;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -113,9 +139,11 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     *skip_flag = (p.status != nullptr && *reinterpret_cast<const volatile int32_t*>(p.status) != 0) ? 1 : 0;
   if (threadIdx.x == 0) {
     mbar_init(bar(Q_FULL), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < KSTAGES; ++s) {
       mbar_init(bar(K_FULL + s), 1);  mbar_init(bar(K_EMPTY + s), 1);
       mbar_init(bar(V_FULL + s), 1);  mbar_init(bar(V_EMPTY + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar(S_FULL + s), 1);  mbar_init(bar(P_FULL + s), BM);
       mbar_init(bar(O_FULL + s), 1);
     }
@@ -144,8 +172,8 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
 #pragma unroll
       for (int x = 0; x < 2; ++x)
 #pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf)
-          tma_load_3d(smem_base + OFF_Q + x * TILE_BYTES + hlf * SUB_BYTES, &tm_q, bar(Q_FULL), hlf * 64, head,
+        for (int hlf = 0; hlf < NSUB; ++hlf)
+          tma_load_3d(smem_base + OFF_Q + x * TILE_BYTES + hlf * SUB_BYTES, &tm_q, bar(Q_FULL), hlf * SUB_ELEMS, head,
                       qo_base + row0 + x * BM);
     }
     __syncwarp();
@@ -166,10 +194,10 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       if (elect_one()) {
         mbar_arrive_expect_tx(bar(K_FULL + ks), TILE_BYTES);
 #pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf) {
+        for (int hlf = 0; hlf < NSUB; ++hlf) {
           const uint32_t dst = smem_base + OFF_K + ks * TILE_BYTES + hlf * SUB_BYTES;
-          if (paged) tma_load_4d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, 0, kvh, page);
-          else tma_load_3d(dst, &tm_k, bar(K_FULL + ks), hlf * 64, kvh, kv_base + j * BN);
+          if (paged) tma_load_4d(dst, &tm_k, bar(K_FULL + ks), hlf * SUB_ELEMS, 0, kvh, page);
+          else tma_load_3d(dst, &tm_k, bar(K_FULL + ks), hlf * SUB_ELEMS, kvh, kv_base + j * BN);
         }
       }
       __syncwarp();
@@ -181,10 +209,10 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         const uint32_t vbar = fix ? bar(V_FIX) : bar(V_FULL + vs);
         mbar_arrive_expect_tx(vbar, TILE_BYTES);
 #pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf) {
+        for (int hlf = 0; hlf < NSUB; ++hlf) {
           const uint32_t dst = smem_base + OFF_V + vs * TILE_BYTES + hlf * SUB_BYTES;
-          if (paged) tma_load_4d(dst, &tm_v, vbar, hlf * 64, 0, kvh, page);
-          else tma_load_3d(dst, &tm_v, vbar, hlf * 64, kvh, kv_base + j * BN);
+          if (paged) tma_load_4d(dst, &tm_v, vbar, hlf * SUB_ELEMS, 0, kvh, page);
+          else tma_load_3d(dst, &tm_v, vbar, hlf * SUB_ELEMS, kvh, kv_base + j * BN);
         }
       }
       __syncwarp();
@@ -195,8 +223,8 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
         if (alive) {
           // whole 128-byte rows are zeroed, so the swizzle does not matter
           unsigned char* vt = smem_gen + OFF_V + vs * TILE_BYTES;
-          for (int c = lane; c < (BN - valid_rows) * 16; c += 32) {
-            const int r = valid_rows + (c >> 4), ch = c & 15;
+          for (int c = lane; c < (BN - valid_rows) * (NSUB * 8); c += 32) {
+            const int r = valid_rows + c / (NSUB * 8), ch = c % (NSUB * 8);
             *reinterpret_cast<uint4*>(vt + (ch >> 3) * SUB_BYTES + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
           }
           fence_proxy_async_smem();
@@ -210,27 +238,32 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     // The whole warp walks the loop (waits are warp-uniform); the tcgen05 instructions are
     // issued by the one lane elect.sync picks, so their operands can live in uniform registers.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false, false);
-    constexpr uint32_t IDESC_PV = idesc_bf16(BM, kHeadDim, false, true);
+    constexpr uint32_t IDESC_QK = F8 ? idesc_e4m3(BM, BN, false, false) : idesc_bf16(BM, BN, false, false);
+    constexpr uint32_t IDESC_PV = F8 ? idesc_e4m3(BM, kHeadDim, false, true) : idesc_bf16(BM, kHeadDim, false, true);
+    constexpr int KSTEPS = F8 ? 4 : 8;              // MMAs per 128-deep contraction (32 bytes of K extent each)
+    constexpr int V_KSTEP = (F8 ? 32 : 16) * 128;   // bytes between the key slices of consecutive P V MMAs
     // descriptor templates: K-major operands (Q, K): LBO unused (16 B), SBO 1024 B;
-    // MN-major V: LBO 16384 B (next 64 columns), SBO 1024 B (next 8 keys)
+    // MN-major V: LBO 16384 B (next sub-tile of head_dim), SBO 1024 B (next 8 keys)
     const uint64_t dk_hi = smem_desc(0, 16, 1024) & 0xFFFFFFFFFFFF0000ull;
-    const uint64_t dv_hi = smem_desc(0, 2 * SUB_BYTES / 2, 1024) & 0xFFFFFFFFFFFF0000ull;
+    const uint64_t dv_hi = smem_desc(0, SUB_BYTES, 1024) & 0xFFFFFFFFFFFF0000ull;
     auto issue_qk = [&](int x, int j) {
       const uint32_t qa = (smem_base + OFF_Q + x * TILE_BYTES) >> 4;
       const uint32_t ka = (smem_base + OFF_K + (j % KSTAGES) * TILE_BYTES) >> 4;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+      for (int k = 0; k < KSTEPS; ++k) {
         const uint32_t o = ((k >> 2) * SUB_BYTES + (k & 3) * 32) >> 4;
-        mma_ss(tmem + x * BN, dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+        if constexpr (F8) mma_ss_f8(tmem + x * BN, dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+        else mma_ss(tmem + x * BN, dk_hi | ((qa + o) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
       }
     };
     auto issue_pv = [&](int x, int j) {
       const uint32_t va = (smem_base + OFF_V + (j % VSTAGES) * TILE_BYTES) >> 4;
 #pragma unroll
-      for (int k = 0; k < 8; ++k)
-        mma_ts(tmem + 256 + x * kHeadDim, tmem + x * BN + k * 8, dv_hi | ((va + k * (2048 >> 4)) & 0x3FFF), IDESC_PV,
-               (j > 0 || k > 0) ? 1u : 0u);
+      for (int k = 0; k < KSTEPS; ++k) {              // P: 8 TMEM columns per MMA in both formats
+        const uint64_t vd = dv_hi | ((va + k * (V_KSTEP >> 4)) & 0x3FFF);
+        if constexpr (F8) mma_ts_f8(tmem + 256 + x * kHeadDim, tmem + x * BN + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        else mma_ts(tmem + 256 + x * kHeadDim, tmem + x * BN + k * 8, vd, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+      }
     };
     bool alive = n_total > 0 ? mbar_wait(bar(Q_FULL), 0, abort_flag, spin_limit) : true;
     if (alive && n_total > 0) {
@@ -299,6 +332,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
     const float scale_log2 = p.sm_scale * kLog2e * (p.k_scale_head ? p.k_scale_head[kvh] : 1.f);
     const bool want_score = (p.flags & MSA_FLAG_OUT_SCORE) != 0 && p.max_score != nullptr;
     float m_used = -INFINITY, l_sum = 0.f;
+    float l_exact = 0.f;                                 // e4m3 only: sum of the unrounded probabilities, for the LSE
     bool alive = true;
 
     for (int j = 0; j < nx && alive; ++j) {
@@ -345,7 +379,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       const float m_cand = fmaxf(m_used, mx * scale_log2);
       const bool bump = (m_cand - m_used) > kRescaleThreshold;      // false for (-inf) - (-inf) = NaN
       float factor = 1.f;
-      if (bump) { factor = exp2_fast(m_used - m_cand); m_used = m_cand; l_sum *= factor; }
+      if (bump) { factor = exp2_fast(m_used - m_cand); m_used = m_cand; l_sum *= factor; l_exact *= factor; }
       if (j > 0 && __any_sync(0xffffffffu, bump)) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -357,7 +391,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
           tmem_st32(tO + c * 32, v);
         }
       }
-      const float msafe = (m_used == -INFINITY) ? 0.f : m_used;
+      const float msafe = ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset;
       if (r == 0) trace(x, j, 3);
       // ---- P = exp2(S * scale - m) as bf16, written over the first half of S ----
       // The special-function unit does 16 exp2 per clock per SM, a quarter of what the tensor
@@ -367,10 +401,11 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       // is done on packed pairs (fma.rn.f32x2 / add.rn.f32x2).
       const uint64_t scale2 = f2_pack(scale_log2, scale_log2);
       const uint64_t negm2 = f2_pack(-msafe, -msafe);
-      uint64_t lsum2 = f2_pack(0.f, 0.f);
+      uint64_t lsum2 = f2_pack(0.f, 0.f), lex2 = f2_pack(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        uint32_t pk[F8 ? 8 : 16];
+        uint16_t held = 0;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])), scale2, negm2);
@@ -396,15 +431,28 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
             p0 = exp2_fast(x0);
             p1 = exp2_fast(x1);
           }
-          lsum2 = f2_add(lsum2, f2_pack(p0, p1));
-          pk[e >> 1] = pack2<false>(p0, p1);
+          if constexpr (F8) {
+            // O is normalised by the sum of the probabilities as the MMA sees them (see the decode kernel);
+            // the LSE reports the sum before rounding
+            lex2 = f2_add(lex2, f2_pack(p0, p1));
+            const uint16_t pr = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
+            const float2 rr = e4m3x2_to_float2(pr);
+            lsum2 = f2_add(lsum2, f2_pack(rr.x, rr.y));
+            if (e & 2) pk[e >> 2] = static_cast<uint32_t>(held) | (static_cast<uint32_t>(pr) << 16);
+            else held = pr;
+          } else {
+            lsum2 = f2_add(lsum2, f2_pack(p0, p1));
+            pk[e >> 1] = pack2<false>(p0, p1);
+          }
         }
-        tmem_st16(tS + c * 16, pk);
+        if constexpr (F8) tmem_st8(tS + c * 8, pk);
+        else tmem_st16(tS + c * 16, pk);
       }
       {
         float l0, l1;
         f2_unpack(lsum2, l0, l1);
         l_sum += l0 + l1;
+        if constexpr (F8) { f2_unpack(lex2, l0, l1); l_exact += l0 + l1; }
       }
       if (r == 0) trace(x, j, 4);
       tmem_wait_st();
@@ -446,7 +494,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       }
       if (row_ok && p.lse)
         p.lse[static_cast<int64_t>(gtok) * p.num_qo_heads + head] =
-            l_sum > 0.f ? m_used * kLn2 + __logf(l_sum) : -INFINITY;
+            l_sum > 0.f ? (m_used - kPOffset) * kLn2 + __logf(F8 ? l_exact : l_sum) : -INFINITY;
     }
   }
 
@@ -517,7 +565,8 @@ int fmha_tc_supported(const MsaFmhaParams& p) {
 
 int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   using namespace tc;
-  if (p.q_dtype != MSA_DT_BF16 || p.kv_dtype != MSA_DT_BF16) return MSA_ERR_UNSUPPORTED;
+  const bool f8 = p.kv_dtype == MSA_DT_E4M3;
+  if (p.q_dtype != p.kv_dtype || (p.kv_dtype != MSA_DT_BF16 && !f8)) return MSA_ERR_UNSUPPORTED;
   if ((p.flags & MSA_FLAG_SPARSE) || p.partial_o || p.pack != 1) return MSA_ERR_UNSUPPORTED;
   if (p.page_size != 0 && p.page_size != BN) return MSA_ERR_UNSUPPORTED;
   const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;
@@ -525,38 +574,46 @@ int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
   if (p.num_work <= 0) return MSA_OK;
 
   CUtensorMap tq, tk, tv;
+  const uint64_t es = f8 ? 1 : 2;                              // bytes per element
+  const uint32_t sub = f8 ? 128 : 64;                          // elements per 128-byte row of a sub-tile
   {
     const uint64_t dims[3] = {128, static_cast<uint64_t>(p.num_qo_heads), static_cast<uint64_t>(p.total_q)};
-    const uint64_t str[2] = {static_cast<uint64_t>(p.q_stride_head) * 2, static_cast<uint64_t>(p.q_stride_tok) * 2};
-    const uint32_t box[3] = {64, 1, BM};
-    if (!make_map(&tq, p.q, 3, dims, str, box)) return MSA_ERR_LAUNCH;
+    const uint64_t str[2] = {static_cast<uint64_t>(p.q_stride_head) * es, static_cast<uint64_t>(p.q_stride_tok) * es};
+    const uint32_t box[3] = {sub, 1, BM};
+    if (!make_map(&tq, p.q, 3, dims, str, box, f8)) return MSA_ERR_LAUNCH;
   }
   if (p.kv_extent <= 0) return MSA_ERR_BAD_ARG;
   const uint64_t big = static_cast<uint64_t>(p.kv_extent);   // rows / pages past it read as zero
   if (p.page_size > 0) {
     const uint64_t dims[4] = {128, BN, static_cast<uint64_t>(p.num_kv_heads), big};
-    const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * 2, static_cast<uint64_t>(p.k_stride_head) * 2,
-                            static_cast<uint64_t>(p.k_stride_page) * 2};
-    const uint64_t vs[3] = {static_cast<uint64_t>(p.v_stride_tok) * 2, static_cast<uint64_t>(p.v_stride_head) * 2,
-                            static_cast<uint64_t>(p.v_stride_page) * 2};
-    const uint32_t box[4] = {64, BN, 1, 1};
-    if (!make_map(&tk, p.k, 4, dims, ks, box) || !make_map(&tv, has_o ? p.v : p.k, 4, dims, has_o ? vs : ks, box)) return MSA_ERR_LAUNCH;
+    const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * es, static_cast<uint64_t>(p.k_stride_head) * es,
+                            static_cast<uint64_t>(p.k_stride_page) * es};
+    const uint64_t vs[3] = {static_cast<uint64_t>(p.v_stride_tok) * es, static_cast<uint64_t>(p.v_stride_head) * es,
+                            static_cast<uint64_t>(p.v_stride_page) * es};
+    const uint32_t box[4] = {sub, BN, 1, 1};
+    if (!make_map(&tk, p.k, 4, dims, ks, box, f8) || !make_map(&tv, has_o ? p.v : p.k, 4, dims, has_o ? vs : ks, box, f8))
+      return MSA_ERR_LAUNCH;
   } else {
     const uint64_t dims[3] = {128, static_cast<uint64_t>(p.num_kv_heads), big};
-    const uint64_t ks[2] = {static_cast<uint64_t>(p.k_stride_head) * 2, static_cast<uint64_t>(p.k_stride_tok) * 2};
-    const uint64_t vs[2] = {static_cast<uint64_t>(p.v_stride_head) * 2, static_cast<uint64_t>(p.v_stride_tok) * 2};
-    const uint32_t box[3] = {64, 1, BN};
-    if (!make_map(&tk, p.k, 3, dims, ks, box) || !make_map(&tv, has_o ? p.v : p.k, 3, dims, has_o ? vs : ks, box)) return MSA_ERR_LAUNCH;
+    const uint64_t ks[2] = {static_cast<uint64_t>(p.k_stride_head) * es, static_cast<uint64_t>(p.k_stride_tok) * es};
+    const uint64_t vs[2] = {static_cast<uint64_t>(p.v_stride_head) * es, static_cast<uint64_t>(p.v_stride_tok) * es};
+    const uint32_t box[3] = {sub, 1, BN};
+    if (!make_map(&tk, p.k, 3, dims, ks, box, f8) || !make_map(&tv, has_o ? p.v : p.k, 3, dims, has_o ? vs : ks, box, f8))
+      return MSA_ERR_LAUNCH;
   }
-  static bool attr_done[16] = {};
+  static bool attr_done[2][16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 16 || !attr_done[dev]) {
-    if (cudaFuncSetAttribute(fmha_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return MSA_ERR_LAUNCH;
-    if (dev < 16) attr_done[dev] = true;
+  if (dev >= 16 || !attr_done[f8][dev]) {
+    const cudaError_t e = f8 ? cudaFuncSetAttribute(fmha_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    Cfg<true>::SMEM_BYTES)
+                             : cudaFuncSetAttribute(fmha_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    Cfg<false>::SMEM_BYTES);
+    if (e != cudaSuccess) return MSA_ERR_LAUNCH;
+    if (dev < 16) attr_done[f8][dev] = true;
   }
-  fmha_tc_kernel<<<p.num_work, NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv, g_knobs);
+  if (f8) fmha_tc_kernel<true><<<p.num_work, NTHREADS, Cfg<true>::SMEM_BYTES, stream>>>(p, tq, tk, tv, g_knobs);
+  else fmha_tc_kernel<false><<<p.num_work, NTHREADS, Cfg<false>::SMEM_BYTES, stream>>>(p, tq, tk, tv, g_knobs);
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
 }
 

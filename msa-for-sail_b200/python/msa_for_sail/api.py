@@ -359,11 +359,11 @@ def _fmha_sail_plan(
         info["_work_host"] = host[:n]
         if splits > 1:
             splits_per_row = upload(spr[:total_q])
-        # second work list in 256-row items for the tcgen05 prefill kernel (bf16, unsplit, one
-        # query head per row tile, ragged K/V or 128-key pages)
+        # second work list in 256-row items for the tcgen05 prefill kernel (q and k both bf16 or
+        # both e4m3, unsplit, one query head per row tile, ragged K/V or 128-key pages)
         info["work_tc"], info["num_work_tc"] = None, 0
         info["tc_preferred"] = False
-        if pack == 1 and max_qo > 128 and not use_fp8_kvcache and page_size in (-1, 0, 128):
+        if pack == 1 and max_qo > 128 and page_size in (-1, 0, 128):
             args_tc = _lib.MsaPlanArgs(
                 a_q.ctypes.data, a_k.ctypes.data, a_o.ctypes.data, batch, num_qo_heads, hkv, 256, 1,
                 1, num_sms, 0)
@@ -375,8 +375,9 @@ def _fmha_sail_plan(
                 wt = arena.take(n_tc * 8, torch.int32)
                 wt.copy_(torch.from_numpy(host_tc[:n_tc].reshape(-1)))
                 info["work_tc"], info["num_work_tc"] = wt, n_tc
-                # with too few items to fill the GPU the split-KV plan of the generic kernel wins
-                info["tc_preferred"] = splits == 1 or n_tc >= num_sms
+                # with far too few items to fill the GPU the split-KV plan of the generic kernel wins
+                # (a 256-row tcgen05 item runs about three times as fast as the same rows there)
+                info["tc_preferred"] = splits == 1 or n_tc * 2 >= num_sms
 
     if splits > 1:
         info["workspace_o"] = arena.take(splits * total_q * orig_num_qo_heads * 128, torch.float32)
@@ -452,7 +453,7 @@ def _fmha_sail_plan_device(qo_segment_lens, kv_segment_lens, num_qo_heads, hkv, 
     row_tiles = max(1, -(-(max_qo * pack) // bm_eff))
     # long bf16 queries on 128-key pages (or ragged K/V): also a list of 256-row items for the tcgen05
     # prefill kernel, one query head per row tile, unsplit
-    want_tc = (not is_sparse and pack == 1 and max_qo > 128 and not use_fp8_kvcache and page_size in (-1, 0, 128)
+    want_tc = (not is_sparse and pack == 1 and max_qo > 128 and page_size in (-1, 0, 128)
                and splits == 1)
     arena = _Arena(given_workspace, dev)
     info = PlanInfo()
@@ -794,7 +795,7 @@ def _fmha_sail(
     p.qo_offset = qo_offset.data_ptr()
     splits = plan["num_kv_splits"]
     use_tc = (plan.get("work_tc") is not None and kv_block_indexes is None
-              and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+              and q.dtype == k.dtype and k.dtype in (torch.bfloat16, torch.float8_e4m3fn)
               and page_size in (0, 128) and _USE_TC and (plan["tc_preferred"] or _FORCE_TC))
     use_split = output_o and splits > 1 and not use_tc
     kernel_out = out                             # what the attention kernel itself writes (bf16)

@@ -466,6 +466,43 @@ def test_fp8_kv_with_bf16_q_and_per_head_scales():
         check_out(out, ref, f"fp8kv-s{splits}", cos_min=FP8_COS, max_abs=0.1)
 
 
+@pytest.mark.parametrize("paged,qo_lens,kv_lens,hq,hk", [
+    (False, [1000, 257, 640], [1000, 1300, 640], 8, 2),     # multi-tile, tails, chunked prefill
+    (True, [700, 1500], [1211, 1500], 4, 2),                # shuffled pages, tail page
+    (True, [2048], [2048], 2, 1),
+    (False, [130, 1, 0], [400, 900, 5], 2, 1),              # a decode row and an empty item in the same call
+])
+def test_fp8_prefill_matches_oracle(paged, qo_lens, kv_lens, hq, hk, kernel_path):
+    """e4m3 q, k and v with per-tensor scales through the prefill kernels: O, LSE and the per-tile scores."""
+    api = _api()
+    g = gen(len(qo_lens) * 1000 + sum(kv_lens) + hq)
+    q_s, k_s, v_s = 0.02, 0.015, 0.01
+    q8, qf = orc.quantize_e4m3(randn_bf16(g, sum(qo_lens), hq, 128), q_s)
+    if paged:
+        kp, vp, table = make_paged(g, kv_lens, hk, 128, dtype=torch.float32)
+        k8, kpf = orc.quantize_e4m3(kp, k_s); v8, vpf = orc.quantize_e4m3(vp, v_s)
+        kf = orc.paged_to_contiguous(kpf, table, kv_lens, 128); vf = orc.paged_to_contiguous(vpf, table, kv_lens, 128)
+        kw = dict(kv_indices=table.to(DEV))
+    else:
+        k8, kf = orc.quantize_e4m3(randn_bf16(g, sum(kv_lens), hk, 128), k_s)
+        v8, vf = orc.quantize_e4m3(randn_bf16(g, sum(kv_lens), hk, 128), v_s)
+        kw = {}
+    ref, ref_lse = orc.attention(qf, kf, vf, qo_lens, kv_lens, hq, hk, return_lse=True)
+    plan = api.fmha_sail_plan(_i32(qo_lens), _i32(kv_lens), hq, num_kv_heads=hk, page_size=128 if paged else -1,
+                              num_kv_splits=1, use_fp8_kvcache=True, output_maxscore=True)
+    lse = torch.full((sum(qo_lens), hq), 7.0, dtype=torch.float32, device=DEV)
+    out, ms = api.fmha_sail(q8.to(DEV), k8.to(DEV), v8.to(DEV), plan, q_scale=q_s, k_scale=k_s, v_scale=v_s,
+                            lse=lse, check_input_valid=True, **kw)
+    check_out(out, ref, "fp8-prefill", cos_min=FP8_COS, max_abs=0.1)
+    l = lse.cpu()
+    fin = ~torch.isinf(ref_lse)
+    assert torch.equal(torch.isinf(l), ~fin)
+    assert torch.allclose(l[fin], ref_lse[fin], atol=2e-3, rtol=1e-3)
+    ref_ms = orc.tile_max_score(qf, kf, qo_lens, kv_lens, hk, ms.shape[1])
+    # the kernel reports raw e4m3 x e4m3 dot products; the scales are the caller's to apply
+    check_score(ms.float() * (q_s * k_s), ref_ms, "fp8-prefill-ms")
+
+
 def test_fp8_onlyscore():
     api = _api()
     g = gen(78)
