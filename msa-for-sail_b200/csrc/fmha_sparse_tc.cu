@@ -29,6 +29,8 @@
 namespace msa {
 int make_tma_map_bf16(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                       const uint32_t* box);
+int make_tma_map_u8(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                    const uint32_t* box);
 
 namespace sparse_tc {
 namespace {
@@ -36,20 +38,31 @@ namespace {
 using namespace tc;
 
 constexpr int BM = 128, BN = 128;
-constexpr int SUB_BYTES = BM * 64 * 2;
-constexpr int TILE_BYTES = 2 * SUB_BYTES;
+constexpr int SUB_BYTES = BM * 128;             // one [128 rows][128 bytes] swizzled sub-tile: 64 bf16 or 128 e4m3 per row
+constexpr int STAGE_BYTES = BM * 256;           // bf16 O of one chunk on its way out
 constexpr int NWG = 3;                          // softmax + epilogue warpgroups; warpgroup x owns chunks c % 3 == x
 constexpr int NSBUF = NWG;                      // S / P buffers in TMEM, one per warpgroup
-constexpr int NQBUF = 2;                        // Q chunk buffers
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = NQBUF * TILE_BYTES;
-constexpr int OFF_V = OFF_K + TILE_BYTES;
-// bf16 O on its way out: [128 rows][256 B] per warpgroup, the 16-byte pieces of a row XOR-ed with
-// (head & 7).  (Two buffers shared by the three warpgroups would leave room for a third Q buffer, but
-// a warpgroup then waits for another one's bulk copies to be read, ~1 000 clocks: slower.)
-constexpr int OFF_STAGE = OFF_V + TILE_BYTES;
-constexpr int OFF_BAR = OFF_STAGE + NWG * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+// F8: Q, K, V (and P) are e4m3 and the MMAs are kind::f8f6f4; otherwise bf16 and kind::f16.  The tiles are
+// half as large in e4m3 and the shared memory that frees holds two more Q chunk buffers.
+template <bool F8>
+struct Cfg {
+  static constexpr int NSUB = F8 ? 1 : 2;                 // sub-tiles per [128][head_dim] tile
+  static constexpr int ROW_BYTES = F8 ? 128 : 256;        // one row of Q
+  static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
+  static constexpr int NQBUF = F8 ? 4 : 2;                // Q chunk buffers
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = NQBUF * TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + TILE_BYTES;
+  // bf16 O on its way out: [128 rows][256 B] per warpgroup, the 16-byte pieces of a row XOR-ed with
+  // (head & 7).  (Two buffers shared by the three warpgroups would leave room for a third bf16 Q buffer,
+  // but a warpgroup then waits for another one's bulk copies to be read, ~1 000 clocks: slower.)
+  static constexpr int OFF_STAGE = OFF_V + TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_STAGE + NWG * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  // P = 2^(s - m + offset) with m the exact maximum of the one tile: at most 2^8 in e4m3 (upstream's
+  // offset, csrc/include/sm80_fmha_sparse_fwd_mainloop.hpp:409), which keeps small probabilities normal
+  static constexpr float kPOffset = F8 ? 8.0f : 0.0f;
+};
 // 512 threads start with 128 registers each (65 536 in all); setmaxnreg then moves them between the
 // roles.  The sum after the moves must stay within what the launch allocated, or the increase
 // never completes: the launcher checks the compiled register count before it launches.
@@ -69,8 +82,8 @@ constexpr uint32_t kEmuMask = 0x5252;
 constexpr uint32_t O_COL = NSBUF * BN;
 // O_FULL has one barrier per warpgroup: a warpgroup that finished P_c may come to wait for O_c while
 // O_{c-2} is the latest completion, and a single barrier would read as "done" (same parity).
-enum Bar { K_FULL = 0, V_FULL = 1, V_FIX = 2, Q_FULL = 3, Q_EMPTY = 5, S_FULL = 7, P_FULL = 10, O_FULL = 13,
-           O_FREE = 16, NUM_BARS = 17 };
+enum Bar { K_FULL = 0, V_FULL = 1, V_FIX = 2, Q_FULL = 3, Q_EMPTY = 7, S_FULL = 11, P_FULL = 14, O_FULL = 17,
+           O_FREE = 20, NUM_BARS = 21 };
 
 #ifdef MSA_DEBUG_HOOKS
 // optional clock trace of one CTA (debugging aid): [6 roles][512 chunks][8 tags]; roles: warpgroups 0-2,
@@ -327,6 +340,7 @@ sparse_merge_kernel(const __nv_bfloat16* __restrict__ po, const float* __restric
 // ------------------------------------------------------------------------------------------
 // attention kernel
 // ------------------------------------------------------------------------------------------
+template <bool F8>
 __global__ void __launch_bounds__(NTHREADS, 1)
 sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -336,6 +350,10 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
   // this launch covers the work items of kv head `part`, or all of them (part < 0)
   const int item_idx = (part >= 0 ? part_start[part] : 0) + static_cast<int>(blockIdx.x);
   if (item_idx >= part_start[part >= 0 ? part + 1 : p.num_kv_heads]) return;   // uniform: before any barrier / TMEM use
+  using C = Cfg<F8>;
+  constexpr int TILE_BYTES = C::TILE_BYTES, NSUB = C::NSUB, NQBUF = C::NQBUF, ROW_BYTES = C::ROW_BYTES;
+  constexpr int OFF_Q = C::OFF_Q, OFF_K = C::OFF_K, OFF_V = C::OFF_V, OFF_STAGE = C::OFF_STAGE, OFF_BAR = C::OFF_BAR;
+  constexpr int SUB_ELEMS = F8 ? 128 : 64;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -410,9 +428,9 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         const uint32_t vbar = fix ? bar(V_FIX) : bar(V_FULL);
         mbar_arrive_expect_tx(vbar, TILE_BYTES);
 #pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf) {
-          tma_load_4d(smem_base + OFF_K + hlf * SUB_BYTES, &tm_k, bar(K_FULL), hlf * 64, 0, kvh, phys);
-          tma_load_4d(smem_base + OFF_V + hlf * SUB_BYTES, &tm_v, vbar, hlf * 64, 0, kvh, phys);
+        for (int hlf = 0; hlf < NSUB; ++hlf) {
+          tma_load_4d(smem_base + OFF_K + hlf * SUB_BYTES, &tm_k, bar(K_FULL), hlf * SUB_ELEMS, 0, kvh, phys);
+          tma_load_4d(smem_base + OFF_V + hlf * SUB_BYTES, &tm_v, vbar, hlf * SUB_ELEMS, 0, kvh, phys);
         }
       }
       __syncwarp();
@@ -421,8 +439,8 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         alive = __all_sync(0xffffffffu, alive);
         if (alive) {
           unsigned char* vt = smem_gen + OFF_V;
-          for (int c = lane; c < (BN - valid_rows) * 16; c += 32) {
-            const int r = valid_rows + (c >> 4), ch = c & 15;
+          for (int c = lane; c < (BN - valid_rows) * (NSUB * 8); c += 32) {
+            const int r = valid_rows + c / (NSUB * 8), ch = c % (NSUB * 8);
             *reinterpret_cast<uint4*>(vt + (ch >> 3) * SUB_BYTES + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
           }
           fence_proxy_async_smem();
@@ -437,7 +455,8 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     // a chunk sits at n * 2 KB and the MMA descriptor steps 2 KB between 8-row groups.  That is
     // 16 boxes per chunk, issued by 16 different lanes spread over the three loader warps (a
     // warp issues the boxes of its lanes one after another).  G < 8: one {64, G, 1} box per token and
-    // half in the plain layout.
+    // half in the plain layout.  e4m3: a row is 128 bytes, so the box {128, 8, 1} of [token][head][128]
+    // is one swizzle atom and unit n sits at n * 1 KB, which is the plain layout.
     const bool unit8 = (G & 7) == 0;
     const int unit = (warp - GATHER_WARP0) + GATHER_WARPS * lane;      // unit n -> warp n % 3, lane n / 3
     const int upt = unit8 ? G / 8 : 1;                      // units per token
@@ -457,48 +476,60 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       const int ntok = min(tpc, item.z - e0);
       if (gt == 0) {
         trace(4, c, 1);
-        mbar_arrive_expect_tx(bar(Q_FULL + x), ntok * G * 256);
+        mbar_arrive_expect_tx(bar(Q_FULL + x), ntok * G * ROW_BYTES);
       }
       if (unit8) {
-        if (ent >= 0)
-          tma_load_4d(smem_base + OFF_Q + x * TILE_BYTES + unit * 2048, &tm_q, bar(Q_FULL + x), 0, kvh * G + (unit % upt) * 8, 0,
-                      ent >> 5);
+        if (ent >= 0) {
+          if constexpr (F8)
+            tma_load_3d(smem_base + OFF_Q + x * TILE_BYTES + unit * 1024, &tm_q, bar(Q_FULL + x), 0, kvh * G + (unit % upt) * 8,
+                        ent >> 5);
+          else
+            tma_load_4d(smem_base + OFF_Q + x * TILE_BYTES + unit * 2048, &tm_q, bar(Q_FULL + x), 0, kvh * G + (unit % upt) * 8, 0,
+                        ent >> 5);
+        }
         ent = entry_of(c + 1);
       } else {
         for (int ti = unit; ti < ntok; ti += GATHER_THREADS) {
           const int tok = entries[e0 + ti] >> 5;
           const uint32_t dst = smem_base + OFF_Q + x * TILE_BYTES + ti * G * 128;
           tma_load_3d(dst, &tm_q, bar(Q_FULL + x), 0, kvh * G, tok);
-          tma_load_3d(dst + SUB_BYTES, &tm_q, bar(Q_FULL + x), 64, kvh * G, tok);
+          if constexpr (!F8) tma_load_3d(dst + SUB_BYTES, &tm_q, bar(Q_FULL + x), 64, kvh * G, tok);
         }
       }
     }
   } else if (warp == MMA_WARP) {
     // =========================== MMA issuer ===========================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false, false);
-    constexpr uint32_t IDESC_PV = idesc_bf16(BM, kHeadDim, false, true);
+    constexpr uint32_t IDESC_QK = F8 ? idesc_e4m3(BM, BN, false, false) : idesc_bf16(BM, BN, false, false);
+    constexpr uint32_t IDESC_PV = F8 ? idesc_e4m3(BM, kHeadDim, false, true) : idesc_bf16(BM, kHeadDim, false, true);
+    constexpr int KSTEPS = F8 ? 4 : 8;              // MMAs per 128-deep contraction (32 bytes of K extent each)
+    constexpr int V_KSTEP = (F8 ? 32 : 16) * 128;   // bytes between the key slices of consecutive P V MMAs
     const uint64_t dk_hi = smem_desc(0, 16, 1024) & 0xFFFFFFFFFFFF0000ull;
     const uint64_t dv_hi = smem_desc(0, SUB_BYTES, 1024) & 0xFFFFFFFFFFFF0000ull;
     // Q: 8-row groups 2 KB apart with the second head_dim half 1 KB after the first (G % 8 == 0),
     // else the plain two-sub-tile layout
-    const bool unit8 = (G & 7) == 0;
+    // (bf16; an e4m3 chunk is a single plain sub-tile)
+    const bool unit8 = !F8 && (G & 7) == 0;
     const uint64_t dq_hi = unit8 ? (smem_desc(0, 16, 2048) & 0xFFFFFFFFFFFF0000ull) : dk_hi;
     const uint32_t q_half = unit8 ? 1024u : static_cast<uint32_t>(SUB_BYTES);
     auto issue_qk = [&](int x, int sb) {
       const uint32_t qa = (smem_base + OFF_Q + x * TILE_BYTES) >> 4, ka = (smem_base + OFF_K) >> 4;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+      for (int k = 0; k < KSTEPS; ++k) {
         const uint32_t o = ((k >> 2) * SUB_BYTES + (k & 3) * 32) >> 4;
         const uint32_t oq = ((k >> 2) * q_half + (k & 3) * 32) >> 4;
-        mma_ss(tmem + sb * BN, dq_hi | ((qa + oq) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+        if constexpr (F8) mma_ss_f8(tmem + sb * BN, dq_hi | ((qa + oq) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
+        else mma_ss(tmem + sb * BN, dq_hi | ((qa + oq) & 0x3FFF), dk_hi | ((ka + o) & 0x3FFF), IDESC_QK, k > 0);
       }
     };
     auto issue_pv = [&](int sb) {
       const uint32_t va = (smem_base + OFF_V) >> 4;
 #pragma unroll
-      for (int k = 0; k < 8; ++k)
-        mma_ts(tmem + O_COL, tmem + sb * BN + k * 8, dv_hi | ((va + k * (2048 >> 4)) & 0x3FFF), IDESC_PV, k > 0 ? 1u : 0u);
+      for (int k = 0; k < KSTEPS; ++k) {              // P: 8 TMEM columns per MMA in both formats
+        const uint64_t vd = dv_hi | ((va + k * (V_KSTEP >> 4)) & 0x3FFF);
+        if constexpr (F8) mma_ts_f8(tmem + O_COL, tmem + sb * BN + k * 8, vd, IDESC_PV, k > 0 ? 1u : 0u);
+        else mma_ts(tmem + O_COL, tmem + sb * BN + k * 8, vd, IDESC_PV, k > 0 ? 1u : 0u);
+      }
     };
     // Two streams share this warp: S_c = Q_c K^T (c may run three chunks ahead of the other stream:
     // S_{c+3} reuses the buffer of P_c, so it must follow P_c V in issue order) and O_d = P_d V (needs P_d
@@ -578,7 +609,7 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
     const bool issuer = (r & (unit_rows - 1)) == 0;
     const int g = r & (G - 1);                                // head within the group
     bool alive = true;
-    unsigned char* my_stage = smem_gen + OFF_STAGE + x * TILE_BYTES + r * 256;
+    unsigned char* my_stage = smem_gen + OFF_STAGE + x * STAGE_BYTES + r * 256;
     int entry_next = (x < n_chunks && item.y + x * tpc + r / G < item.z) ? entries[item.y + x * tpc + r / G] : 0;
     for (int c = x; c < n_chunks && alive; c += NWG) {
       const int u = c / NWG;
@@ -616,14 +647,15 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
         for (int e = 0; e < 32; e += 2)
           mxs[(e >> 1) & 3] = max3(mxs[(e >> 1) & 3], __uint_as_float(sv[cc][e]), __uint_as_float(sv[cc][e + 1]));
       const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * scale_log2;
-      const float msafe = (mx == -INFINITY) ? 0.f : mx;
+      const float msafe = ((mx == -INFINITY) ? 0.f : mx) - C::kPOffset;
       const uint64_t scale2 = f2_pack(scale_log2, scale_log2);
       const uint64_t negm2 = f2_pack(-msafe, -msafe);
       uint64_t lsum2 = f2_pack(0.f, 0.f);
       if (r == 0) trace(x, c, 3);
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
-        uint32_t pk[16];
+        uint32_t pk[F8 ? 8 : 16];
+        uint16_t held = 0;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sv[cc][e]), __uint_as_float(sv[cc][e + 1])), scale2, negm2);
@@ -647,9 +679,16 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
             p1 = exp2_fast(x1);
           }
           lsum2 = f2_add(lsum2, f2_pack(p0, p1));
-          pk[e >> 1] = pack2<false>(p0, p1);
+          if constexpr (F8) {
+            const uint16_t pr = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
+            if (e & 2) pk[e >> 2] = static_cast<uint32_t>(held) | (static_cast<uint32_t>(pr) << 16);
+            else held = pr;
+          } else {
+            pk[e >> 1] = pack2<false>(p0, p1);
+          }
         }
-        tmem_st16(tS + cc * 16, pk);
+        if constexpr (F8) tmem_st8(tS + cc * 8, pk);
+        else tmem_st16(tS + cc * 16, pk);
       }
       float l0, l1;
       f2_unpack(lsum2, l0, l1);
@@ -699,7 +738,7 @@ sparse_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant_
       fence_proxy_async_smem();                               // generic-proxy writes -> read by the bulk copy
       __syncwarp();
       if (issuer && row_ok) {
-        bulk_store(partial_o + prow * kHeadDim, smem_base + OFF_STAGE + x * TILE_BYTES + r * 256, unit_rows * 256);
+        bulk_store(partial_o + prow * kHeadDim, smem_base + OFF_STAGE + x * STAGE_BYTES + r * 256, unit_rows * 256);
         tma_store_commit();
       }
       if (r == 0) trace(x, c, 7);
@@ -727,7 +766,8 @@ int64_t fmha_sparse_tc_workspace_bytes(int64_t total_q, int num_qo_heads, int nu
 int fmha_sparse_tc_supported(const MsaFmhaParams& p) {
   if (!(p.flags & MSA_FLAG_SPARSE) || !(p.flags & MSA_FLAG_OUT_O) || (p.flags & MSA_FLAG_OUT_SCORE)) return 0;
   if (!p.sparse_ws || !p.page_batch || p.num_logical_pages <= 0) return 0;
-  if (p.q_dtype != MSA_DT_BF16 || p.kv_dtype != MSA_DT_BF16 || p.page_size != sparse_tc::BN) return 0;
+  if (p.q_dtype != p.kv_dtype || (p.kv_dtype != MSA_DT_BF16 && p.kv_dtype != MSA_DT_E4M3)) return 0;
+  if (p.page_size != sparse_tc::BN) return 0;
   const int G = p.num_qo_heads / p.num_kv_heads;
   if (G < 1 || G > 128 || (128 % G) != 0 || p.kv_block_num > 32 || p.total_q >= (1 << 26)) return 0;
   // row indices of the partial buffer are int32 TMA coordinates
@@ -785,40 +825,51 @@ int fmha_sparse_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
 
   // 2. attention over (page, token chunk) items
   CUtensorMap tq, tk, tv;
+  const bool f8 = p.kv_dtype == MSA_DT_E4M3;
+  const uint64_t es = f8 ? 1 : 2;                              // bytes per element
+  const uint32_t sub = f8 ? 128 : 64;                          // elements per 128-byte row of a sub-tile
+  auto make_map = f8 ? make_tma_map_u8 : make_tma_map_bf16;
   {
-    if ((G & 7) == 0) {       // [token][half][head][64]: one box carries both halves of 8 rows
+    if ((G & 7) == 0 && !f8) {       // [token][half][head][64]: one box carries both halves of 8 rows
       const uint64_t dims[4] = {64, static_cast<uint64_t>(p.num_qo_heads), 2, static_cast<uint64_t>(p.total_q)};
       const uint64_t str[3] = {static_cast<uint64_t>(p.q_stride_head) * 2, 128, static_cast<uint64_t>(p.q_stride_tok) * 2};
       const uint32_t box[4] = {64, 8, 2, 1};
       if (make_tma_map_bf16(&tq, p.q, 4, dims, str, box) != MSA_OK) return MSA_ERR_LAUNCH;
     } else {
       const uint64_t dims[3] = {128, static_cast<uint64_t>(p.num_qo_heads), static_cast<uint64_t>(p.total_q)};
-      const uint64_t str[2] = {static_cast<uint64_t>(p.q_stride_head) * 2, static_cast<uint64_t>(p.q_stride_tok) * 2};
-      const uint32_t box[3] = {64, static_cast<uint32_t>(G), 1};
-      if (make_tma_map_bf16(&tq, p.q, 3, dims, str, box) != MSA_OK) return MSA_ERR_LAUNCH;
+      const uint64_t str[2] = {static_cast<uint64_t>(p.q_stride_head) * es, static_cast<uint64_t>(p.q_stride_tok) * es};
+      const uint32_t box[3] = {sub, static_cast<uint32_t>((G & 7) == 0 ? 8 : G), 1};
+      if (make_map(&tq, p.q, 3, dims, str, box) != MSA_OK) return MSA_ERR_LAUNCH;
     }
     const uint64_t kd[4] = {128, BN, static_cast<uint64_t>(p.num_kv_heads), static_cast<uint64_t>(p.kv_extent)};
-    const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * 2, static_cast<uint64_t>(p.k_stride_head) * 2,
-                            static_cast<uint64_t>(p.k_stride_page) * 2};
-    const uint64_t vs[3] = {static_cast<uint64_t>(p.v_stride_tok) * 2, static_cast<uint64_t>(p.v_stride_head) * 2,
-                            static_cast<uint64_t>(p.v_stride_page) * 2};
-    const uint32_t kbox[4] = {64, BN, 1, 1};
-    if (make_tma_map_bf16(&tk, p.k, 4, kd, ks, kbox) != MSA_OK || make_tma_map_bf16(&tv, p.v, 4, kd, vs, kbox) != MSA_OK)
+    const uint64_t ks[3] = {static_cast<uint64_t>(p.k_stride_tok) * es, static_cast<uint64_t>(p.k_stride_head) * es,
+                            static_cast<uint64_t>(p.k_stride_page) * es};
+    const uint64_t vs[3] = {static_cast<uint64_t>(p.v_stride_tok) * es, static_cast<uint64_t>(p.v_stride_head) * es,
+                            static_cast<uint64_t>(p.v_stride_page) * es};
+    const uint32_t kbox[4] = {sub, BN, 1, 1};
+    if (make_map(&tk, p.k, 4, kd, ks, kbox) != MSA_OK || make_map(&tv, p.v, 4, kd, vs, kbox) != MSA_OK)
       return MSA_ERR_LAUNCH;
   }
-  static bool attr_done[16] = {};
+  static bool attr_done[2][16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 16 || !attr_done[dev]) {
+  const int smem_bytes = f8 ? Cfg<true>::SMEM_BYTES : Cfg<false>::SMEM_BYTES;
+  if (dev >= 16 || !attr_done[f8][dev]) {
     // setmaxnreg can only hand out what the launch allocated: threads x compiled registers
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, sparse_tc_kernel) != cudaSuccess || fa.numRegs * NTHREADS < REGS_NEEDED) return MSA_ERR_LAUNCH;
-    if (cudaFuncSetAttribute(sparse_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return MSA_ERR_LAUNCH;
-    if (dev < 16) attr_done[dev] = true;
+    const cudaError_t e1 = f8 ? cudaFuncGetAttributes(&fa, sparse_tc_kernel<true>) : cudaFuncGetAttributes(&fa, sparse_tc_kernel<false>);
+    if (e1 != cudaSuccess || fa.numRegs * NTHREADS < REGS_NEEDED) return MSA_ERR_LAUNCH;
+    const cudaError_t e2 = f8 ? cudaFuncSetAttribute(sparse_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)
+                              : cudaFuncSetAttribute(sparse_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e2 != cudaSuccess) return MSA_ERR_LAUNCH;
+    if (dev < 16) attr_done[f8][dev] = true;
   }
-  sparse_tc_kernel<<<static_cast<unsigned>(w.max_items), NTHREADS, SMEM_BYTES, stream>>>(p, tq, tk, tv, w.items, w.part_start, -1,
-                                                                                     w.entries, w.partial_lse, w.partial_o);
+  if (f8)
+    sparse_tc_kernel<true><<<static_cast<unsigned>(w.max_items), NTHREADS, smem_bytes, stream>>>(
+        p, tq, tk, tv, w.items, w.part_start, -1, w.entries, w.partial_lse, w.partial_o);
+  else
+    sparse_tc_kernel<false><<<static_cast<unsigned>(w.max_items), NTHREADS, smem_bytes, stream>>>(
+        p, tq, tk, tv, w.items, w.part_start, -1, w.entries, w.partial_lse, w.partial_o);
   if (cudaGetLastError() != cudaSuccess) return MSA_ERR_LAUNCH;
 
   // 3. merge the kv_block_num partials of every (token, head).  (Running the merge of kv head k on a

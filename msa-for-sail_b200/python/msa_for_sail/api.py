@@ -826,8 +826,8 @@ def _fmha_sail(
         p.kv_block_num = kv_block_indexes.shape[2]
         p.token_batch = plan["token_batch"].data_ptr()
         g = num_qo_heads // num_kv_heads
-        if (_USE_SPARSE_TC and (plan["sparse_tc_preferred"] or _FORCE_SPARSE_TC) and q.dtype == torch.bfloat16
-                and k.dtype == torch.bfloat16 and page_size == 128 and 128 % g == 0 and p.kv_block_num <= 32
+        if (_USE_SPARSE_TC and (plan["sparse_tc_preferred"] or _FORCE_SPARSE_TC) and q.dtype == k.dtype
+                and k.dtype in (torch.bfloat16, torch.float8_e4m3fn) and page_size == 128 and 128 % g == 0 and p.kv_block_num <= 32
                 and plan["num_logical_pages"] > 0):
             need = _lib.lib.msa_sparse_workspace_bytes(nnz_qo, num_qo_heads, num_kv_heads, p.kv_block_num,
                                                        plan["num_logical_pages"])

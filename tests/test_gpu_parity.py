@@ -421,6 +421,10 @@ def test_sparse_golden(sparse_path):
     ([1, 1, 1], [3000, 129, 5000], 64, 8, 16, 4, False),     # same on a bf16 cache
     ([2, 1], [1000, 4100], 32, 2, 8, 1, True),               # e4m3, 16 rows per item, two tokens
     ([40, 3], [6000, 4500], 8, 2, 32, 1, False),             # 32 selected pages per token
+    ([300, 77], [1500, 700], 8, 2, 8, 1, True),              # e4m3 prefill: many tokens per page, tail pages
+    ([200], [1100], 16, 1, 16, 1, True),                     # e4m3, h_r = 16
+    ([500], [3000], 2, 2, 4, 1, True),                       # e4m3, h_r = 1
+    ([600, 5], [2600, 900], 64, 8, 16, 1, True),             # e4m3, h_r = 8, more chunks than Q buffers per item
 ])
 def test_sparse_matches_oracle(qo_lens, kv_lens, hq, hk, kbn, splits, fp8, sparse_path):
     api = _api()
