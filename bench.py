@@ -55,6 +55,9 @@ WORKLOADS = {
     "msa_prefill_b1_s8192_h32kv4_top16": ("msa_prefill", dict(b=1, t=8192, hq=32, hk=4, topk=16)),          # small: ncu
     "paged_prefill_b4_s8192_h64kv8": ("prefill", dict(b=4, ql=8192, kl=8192, hq=64, hk=8)),                 # config 2
     "paged_prefill_b2_s4096_h32kv4": ("prefill", dict(b=2, ql=4096, kl=4096, hq=32, hk=4)),                 # small: ncu
+    # configs 2 and 3 with e4m3 Q, K, V (upstream's fp8 mode: same shapes, cache and queries cast to e4m3)
+    "paged_prefill_e4m3_b4_s8192_h64kv8": ("prefill", dict(b=4, ql=8192, kl=8192, hq=64, hk=8, fp8=True)),
+    "msa_prefill_e4m3_b2_s32768_h64kv8_top16": ("msa_prefill", dict(b=2, t=32768, hq=64, hk=8, topk=16, fp8=True)),
     "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4": (
         "msa_decode", dict(b=32, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=True)),                     # config 4
     "msa_decode_bf16_b32_kv131072_h64kv8_top16_split4": (
@@ -70,6 +73,8 @@ SUB_CONFIGS = [                       # sub-records of the default run, in BASEL
     ("config2", "paged_prefill_b4_s8192_h64kv8"),
     ("config4", "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4"),
     ("config5", "paged_decode_b1_kv1048576_h64kv8"),
+    ("config2_e4m3", "paged_prefill_e4m3_b4_s8192_h64kv8"),
+    ("config3_e4m3", "msa_prefill_e4m3_b2_s32768_h64kv8_top16"),
 ]
 METRICS = {"prefill": ("prefill_effective_tflops", "TFLOP/s"), "msa_prefill": ("msa_prefill_effective_tflops", "TFLOP/s"),
            "msa_decode": ("msa_decode_kv_gbps", "GB/s"), "decode": ("decode_kv_gbps", "GB/s")}
@@ -215,18 +220,20 @@ def _i32(x):
     return torch.tensor(x, dtype=torch.int32)
 
 
-def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk, **_):
+def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk, fp8=False, **_):
     from oracle import msa_oracle as orc
     g = torch.Generator(device="cpu").manual_seed(seed)
     P = kl // PAGE                                            # pages per sequence
     pool = b * P
-    q_h = (torch.randn(b * ql, hq, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
-    k_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
-    v_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16       # e4m3: plain casts (unit scales)
+    esz = 1 if fp8 else 2
+    q_h = (torch.randn(b * ql, hq, D, generator=g) * 0.5).to(torch.bfloat16).to(dt).pin_memory()
+    k_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).to(dt).pin_memory()
+    v_h = (torch.randn(pool, hk, PAGE, D, generator=g) * 0.5).to(torch.bfloat16).to(dt).pin_memory()
     # device-timed step: the page tables are one seeded random permutation of the whole pool
     table = torch.randperm(pool, generator=g).to(torch.int32).to(dev)
     q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
-    plan = msa.fmha_sail_plan(_i32([ql] * b), _i32([kl] * b), hq, num_kv_heads=hk, page_size=PAGE)
+    plan = msa.fmha_sail_plan(_i32([ql] * b), _i32([kl] * b), hq, num_kv_heads=hk, page_size=PAGE, use_fp8_kvcache=fp8)
     out = torch.empty(b * ql, hq, D, dtype=torch.bfloat16, device=dev)
     lse = torch.empty(b * ql, hq, dtype=torch.float32, device=dev)
     out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
@@ -245,7 +252,8 @@ def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk, **_):
     local = torch.stack([torch.cat([torch.randperm(gp, generator=g) + j * gp for j in range(NCH)])
                          for _ in range(b)]).to(torch.int32)
     cq = ql // NCH
-    plans = [msa.fmha_sail_plan(_i32([cq]), _i32([(j + 1) * cq]), hq, num_kv_heads=hk, page_size=PAGE) for j in range(NCH)]
+    plans = [msa.fmha_sail_plan(_i32([cq]), _i32([(j + 1) * cq]), hq, num_kv_heads=hk, page_size=PAGE, use_fp8_kvcache=fp8)
+             for j in range(NCH)]
     local_dev = local.to(dev)
     table_e2e = (local + torch.arange(b, dtype=torch.int32).view(b, 1) * P).reshape(-1).to(dev)
 
@@ -291,27 +299,27 @@ def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk, **_):
         outs, refs, lses, lrefs = [], [], [], []
         for bi, kh in units:
             pages = table[bi * P:(bi + 1) * P].long()
-            kc = k[pages, kh].reshape(P * PAGE, 1, D).cpu()
-            vc = v[pages, kh].reshape(P * PAGE, 1, D).cpu()
+            kc = k[pages, kh].reshape(P * PAGE, 1, D).to(torch.bfloat16).cpu()      # e4m3 values are exact in bf16
+            vc = v[pages, kh].reshape(P * PAGE, 1, D).to(torch.bfloat16).cpu()
             pos = torch.randint(0, ql, (toks_per_unit,), generator=gen).tolist()
             pos[0] = ql - 1                                                    # the longest row of the sequence
             for i in pos:
                 t = bi * ql + i
-                qq = q[t:t + 1, kh * gsz:(kh + 1) * gsz].cpu()
+                qq = q[t:t + 1, kh * gsz:(kh + 1) * gsz].to(torch.bfloat16).cpu()
                 o_ref, l_ref = orc.attention_single(qq, kc, vc, gsz, 1, True, i + kl - ql, return_lse=True)
                 outs.append(out[t:t + 1, kh * gsz:(kh + 1) * gsz].cpu()); refs.append(o_ref)
                 lses.append(lse[t:t + 1, kh * gsz:(kh + 1) * gsz].cpu()); lrefs.append(l_ref)
-        r = _compare_rows(torch.cat(outs), torch.cat(refs), 0.9999, 2e-2, "dense prefill O")
+        r = _compare_rows(torch.cat(outs), torch.cat(refs), 0.999 if fp8 else 0.9999, 0.1 if fp8 else 2e-2, "dense prefill O")
         lerr = (torch.cat(lses) - torch.cat(lrefs)).abs().max().item()
         if lerr > 2e-2:
             raise ParityError(f"dense prefill LSE off by {lerr:.4g}")
         r["lse_max_abs"] = lerr
         return r
 
-    nbytes = (q.numel() + k.numel() + v.numel() + out.numel()) * 2
+    nbytes = (q.numel() + k.numel() + v.numel()) * esz + out.numel() * 2
     return dict(step=step, e2e_step=e2e_step, e2e_ref_step=e2e_ref_step, results=(out, out_h), parity=parity,
                 flops=attention_flops(b, ql, kl, hq), bytes=nbytes, unit="TFLOP/s", bound="tensor", launches=1, graph=False, tokens=b * ql,
-                h2d=(q_h.numel() + k_h.numel() + v_h.numel()) * 2, d2h=out_h.numel() * 2,
+                h2d=(q_h.numel() + k_h.numel() + v_h.numel()) * esz, d2h=out_h.numel() * 2,
                 e2e_note=("chunked prefill through the public API, four row chunks per sequence; the copy-in of a chunk's Q "
                           "rows and K/V pages from pinned host memory, its attention and the copy-out of its O overlap "
                           "with the neighbouring chunks on three streams; this leg shuffles the page table within the "
@@ -320,7 +328,7 @@ def setup_prefill(msa, dev, seed, b, ql, kl, hq, hk, **_):
                 l2="inputs larger than L2 (Q+K+V+O = %.2f GB per GPU)" % (nbytes / 1e9))
 
 
-def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, **_):
+def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, fp8=False, **_):
     """Configs 1 and 3: 1-head proxy max-score pass -> page top-k -> sparse attention on the selection.
     K = N(0,1) + one offset ~ N(0, koff) per (page, head), broadcast over the page's keys and head_dim."""
     from oracle import msa_oracle as orc
@@ -330,11 +338,15 @@ def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, **_):
     kp = (torch.randn(b * P, hk, PAGE, D, device=dev, generator=g)
           + math.sqrt(koff) * torch.randn(b * P, hk, 1, 1, device=dev, generator=g)).to(torch.bfloat16)
     vp = torch.randn(b * P, hk, PAGE, D, device=dev, generator=g).to(torch.bfloat16)
+    if fp8:                                                   # plain casts (unit scales); the page offsets stay within range
+        q, kp, vp = q.to(torch.float8_e4m3fn), kp.to(torch.float8_e4m3fn), vp.to(torch.float8_e4m3fn)
+    esz = 1 if fp8 else 2
+    wide = (lambda x: x.to(torch.bfloat16)) if fp8 else (lambda x: x)          # e4m3 values are exact in bf16
     table = torch.randperm(b * P, device=dev, generator=g).to(torch.int32)
     qx, kx = q[:, :1].contiguous(), kp[:, :1].contiguous()
     lens = _i32([t] * b)
-    plan1 = msa.fmha_sail_plan(lens, lens, 1, num_kv_heads=1, page_size=PAGE, output_maxscore=True)
-    plan2 = msa.fmha_sail_plan(lens, lens, hq, num_kv_heads=hk, page_size=PAGE, kv_block_num=topk)
+    plan1 = msa.fmha_sail_plan(lens, lens, 1, num_kv_heads=1, page_size=PAGE, output_maxscore=True, use_fp8_kvcache=fp8)
+    plan2 = msa.fmha_sail_plan(lens, lens, hq, num_kv_heads=hk, page_size=PAGE, kv_block_num=topk, use_fp8_kvcache=fp8)
     ms = torch.full((1, plan1[3]["max_k_tiles"], b * t), -float("inf"), device=dev)
     idx = torch.empty(b * t, 1, topk, dtype=torch.int32, device=dev)
     out = torch.empty(b * t, hq, D, dtype=torch.bfloat16, device=dev)
@@ -366,8 +378,8 @@ def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, **_):
     cplans = []
     for j in range(NCH):
         ln_q, ln_k = _i32([cq]), _i32([(j + 1) * cq])
-        pa = msa.fmha_sail_plan(ln_q, ln_k, 1, num_kv_heads=1, page_size=PAGE, output_maxscore=True)
-        pb = msa.fmha_sail_plan(ln_q, ln_k, hq, num_kv_heads=hk, page_size=PAGE, kv_block_num=topk)
+        pa = msa.fmha_sail_plan(ln_q, ln_k, 1, num_kv_heads=1, page_size=PAGE, output_maxscore=True, use_fp8_kvcache=fp8)
+        pb = msa.fmha_sail_plan(ln_q, ln_k, hq, num_kv_heads=hk, page_size=PAGE, kv_block_num=topk, use_fp8_kvcache=fp8)
         cplans.append((pa, pb, torch.full((1, pa[3]["max_k_tiles"], cq), -float("inf"), device=dev)))
     cidx = torch.empty(cq, 1, topk, dtype=torch.int32, device=dev)
     qd, od = torch.empty_like(q), torch.empty_like(out)
@@ -415,8 +427,8 @@ def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, **_):
         for j, tk in enumerate(toks):
             s, i = int(seq[j]), int(pos[j])
             if s not in kseq:
-                kseq[s] = kx[table[s * P:(s + 1) * P].long(), 0].reshape(P * PAGE, D).float().cpu()
-            sc = kseq[s][:i + 1] @ qx[tk, 0].float().cpu()
+                kseq[s] = wide(kx[table[s * P:(s + 1) * P].long(), 0]).reshape(P * PAGE, D).float().cpu()
+            sc = kseq[s][:i + 1] @ wide(qx[tk, 0]).float().cpu()
             npg = i // PAGE + 1
             sc = torch.nn.functional.pad(sc, (0, npg * PAGE - (i + 1)), value=-float("inf"))
             ms_ref[j, :npg] = sc.view(npg, PAGE).max(-1).values
@@ -434,14 +446,14 @@ def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, **_):
             lp = sel_gpu[j].long()
             valid = lp >= 0
             phys = table[s * P + lp.clamp_min(0).to(dev)].long()
-            kc.append(kp[phys].cpu()); vc.append(vp[phys].cpu())
+            kc.append(wide(kp[phys]).cpu()); vc.append(wide(vp[phys]).cpu())
             mini = torch.zeros(P, dtype=torch.int32)
             mini[lp[valid]] = (torch.arange(topk)[valid] + j * topk).to(torch.int32)
             tabs.append(mini)
-        ref = orc.sparse_attention(q[toks].cpu(), torch.cat(kc), torch.cat(vc), [1] * n_tok, [t] * n_tok, torch.cat(tabs),
+        ref = orc.sparse_attention(wide(q[toks]).cpu(), torch.cat(kc), torch.cat(vc), [1] * n_tok, [t] * n_tok, torch.cat(tabs),
                                    sel_gpu.view(n_tok, 1, topk).expand(n_tok, hk, topk), hq,
                                    qo_offset=[int(x) for x in pos])
-        r = _compare_rows(out[toks].cpu(), ref, 0.9999, 2e-2, "sparse prefill O")
+        r = _compare_rows(out[toks].cpu(), ref, 0.999 if fp8 else 0.9999, 0.1 if fp8 else 2e-2, "sparse prefill O")
         r.update(topk_exact=topk_exact, topk_rows=n_tok, score_rel_err=score_err)
         return r
 
@@ -450,7 +462,7 @@ def setup_msa_prefill(msa, dev, seed, b, t, hq, hk, topk, koff=2.0, **_):
                             topk=(s_topk, ms[:, :P].numel() * 4 + idx.numel() * 4, "GB/s"),
                             sparse=(s_sparse, f_sparse, "TFLOP/s")),
                 unit="TFLOP/s", bound="tensor", launches=7, graph=False, tokens=b * t,
-                h2d=q_h.numel() * 2, d2h=out_h.numel() * 2,
+                h2d=q_h.numel() * esz, d2h=out_h.numel() * 2,
                 e2e_note=("chunked prefill through the public API, %d row chunk(s) per sequence: the copy-in of a chunk's Q "
                           "from pinned host memory, its proxy pass, top-k and sparse attention and the copy-out of its O "
                           "overlap with the neighbouring chunks on three streams; the KV cache is device-resident state" % NCH),
@@ -972,9 +984,12 @@ def measure(msa, workload, args, rank, world, local_rank, dev, steps, warmup, wi
         timed_s = total_ms * 1e-3
         if wl["bound"] == "tensor":
             burst = timed_s < 1.0
-            peak = pk["bf16"] if burst else pk["bf16_sustained"]
+            f8x = 2.0 if w.get("fp8") else 1.0
+            peak = f8x * (pk["bf16"] if burst else pk["bf16_sustained"])
             psrc = pk["src"] + (" cuBLAS bf16, burst figure: the timed region lasts %.2f s" % timed_s if burst else
                                 " cuBLAS bf16, sustained figure: the timed region lasts %.2f s" % timed_s)
+            if w.get("fp8"):
+                psrc += "; x 2 for e4m3 (no fp8 GEMM was measured on this pool: twice the bf16 figure, as the nominal peaks are)"
         else:
             peak, psrc = pk["hbm"], pk["src"] + " (STREAM-style copy)"
         achieved = work / (step_ms * 1e-3)
@@ -984,8 +999,8 @@ def measure(msa, workload, args, rank, world, local_rank, dev, steps, warmup, wi
                 "traffic_source": TRAFFIC.get(workload, (None, "not captured"))[1] if world == 1 else "single-GPU captures only",
                 "peak_source": psrc, "step_ms": step_ms}
         if wl["bound"] == "tensor":
-            roof["frac_of_burst_peak"] = achieved / pk["bf16"]
-            roof["frac_of_sustained_peak"] = achieved / pk["bf16_sustained"]
+            roof["frac_of_burst_peak"] = achieved / (f8x * pk["bf16"])
+            roof["frac_of_sustained_peak"] = achieved / (f8x * pk["bf16_sustained"])
         cfg = config_of(workload, world, not args.no_graph)
         rec = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -1053,8 +1068,9 @@ def main():
             kind = WORKLOADS[name][0]
             # short steps need more of them for a stable mean and for the clock sampler to see the region
             steps = args.steps if kind in ("prefill", "msa_prefill") else max(args.steps, 200 if kind == "msa_decode" else 50)
+            # (the e4m3 variants share the CPU baseline of configs 2 and 3: same algorithm, same shapes)
             rec, err = measure(msa, name, args, rank, world, local_rank, dev, steps, args.warmup,
-                               not args.no_cpu_baseline)
+                               not args.no_cpu_baseline and not label.endswith("_e4m3"))
             if err:
                 failures.append(f"{name}: {err}")
             subs[label] = rec

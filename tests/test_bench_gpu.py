@@ -69,6 +69,32 @@ def test_msa_prefill_parity_sample_with_page_offsets(hq, hk, topk):
     assert r["topk_exact"] and r["max_abs"] <= 2e-2 and r["cos"] >= 0.9999
 
 
+def test_e4m3_prefill_workloads_parity_sample_and_end_to_end():
+    """The e4m3 variants of the dense and the sparse prefill workloads at reduced sizes: parity sample of the
+    timed step, and the chunked end-to-end leg against the resident call."""
+    import bench
+    import msa_for_sail as msa
+    dev = torch.device("cuda:0")
+    wl = bench.setup_prefill(msa, dev, 9, b=2, ql=2048, kl=2048, hq=16, hk=2, fp8=True)
+    wl["step"]()
+    r = wl["parity"]()
+    assert r["rows"] >= 64 and r["cos"] >= 0.999
+    wl["e2e_ref_step"](); wl["e2e_step"](); wl["e2e_step"]()
+    torch.cuda.synchronize()
+    out, out_h = wl["results"]
+    assert torch.nn.functional.cosine_similarity(out_h.float().flatten(), out.float().cpu().flatten(), dim=0).item() >= 0.9999
+    del wl
+    wl = bench.setup_msa_prefill(msa, dev, 10, b=2, t=4096, hq=64, hk=8, topk=16, fp8=True)
+    wl["step"]()
+    r = wl["parity"]()
+    assert r["topk_exact"] and r["cos"] >= 0.999
+    wl["e2e_step"](); wl["e2e_step"]()
+    torch.cuda.synchronize()
+    out, out_h = wl["results"]
+    assert torch.isfinite(out_h.float()).all()
+    assert torch.nn.functional.cosine_similarity(out_h.float().flatten(), out.float().cpu().flatten(), dim=0).item() >= 0.9999
+
+
 @pytest.mark.parametrize("fp8", [True, False])
 def test_msa_decode_parity_sample(fp8):
     """The decode pipeline in the shape of the target configuration (many batch items, 1 024-page
