@@ -58,6 +58,8 @@ WORKLOADS = {
     # configs 2 and 3 with e4m3 Q, K, V (upstream's fp8 mode: same shapes, cache and queries cast to e4m3)
     "paged_prefill_e4m3_b4_s8192_h64kv8": ("prefill", dict(b=4, ql=8192, kl=8192, hq=64, hk=8, fp8=True)),
     "msa_prefill_e4m3_b2_s32768_h64kv8_top16": ("msa_prefill", dict(b=2, t=32768, hq=64, hk=8, topk=16, fp8=True)),
+    "paged_prefill_e4m3_b2_s4096_h32kv4": ("prefill", dict(b=2, ql=4096, kl=4096, hq=32, hk=4, fp8=True)),       # small: ncu
+    "msa_prefill_e4m3_b1_s8192_h32kv4_top16": ("msa_prefill", dict(b=1, t=8192, hq=32, hk=4, topk=16, fp8=True)), # small: ncu
     "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4": (
         "msa_decode", dict(b=32, kl=131072, hq=64, hk=8, topk=16, splits=4, fp8=True)),                     # config 4
     "msa_decode_bf16_b32_kv131072_h64kv8_top16_split4": (
