@@ -92,6 +92,11 @@ TRAFFIC = {
     "msa_prefill_b1_s8192_h32kv4_top16": (1.055e9, "captured (sparse_tc_kernel; sparse_merge_kernel: 1.155e9)"),
     "msa_prefill_b2_s32768_h64kv8_top16": (16.9e9, "scaled x16 from the b1_s8192_h32kv4 capture (sparse_tc_kernel; "
                                                     "sparse_merge_kernel: 18.5e9)"),
+    "msa_prefill_e4m3_b1_s8192_h32kv4_top16": (0.976e9, "captured (sparse_tc_kernel<e4m3>: 62 MB read + 914 MB written)"),
+    "msa_prefill_e4m3_b2_s32768_h64kv8_top16": (15.6e9, "scaled x16 from the e4m3 b1_s8192_h32kv4 capture (sparse_tc_kernel<e4m3>; "
+                                                         "the merge kernel is the bf16 path's: 18.5e9)"),
+    "paged_prefill_e4m3_b2_s4096_h32kv4": (59.2e6, "captured"),
+    "paged_prefill_e4m3_b4_s8192_h64kv8": (0.47e9, "scaled x8.0 from the e4m3 b2_s4096_h32kv4 capture (59.2 MB)"),
     "msa_decode_e4m3_b8_kv131072_h64kv8_top16_split4": (138.1e6, "captured (score_gemv_kernel; decode_tc_kernel: 33.9e6)"),
     "msa_decode_e4m3_b32_kv131072_h64kv8_top16_split4": (552e6, "scaled x4 from the b8 capture (score_gemv_kernel; "
                                                                "decode_tc_kernel: 135e6)"),
