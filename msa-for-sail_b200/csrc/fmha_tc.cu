@@ -29,6 +29,7 @@
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, reports
 // MSA_STATUS_TIMEOUT in the status word, releases its TMEM and exits.
 #include <mutex>
+#include <type_traits>
 
 #include "tc_ptx.cuh"
 
@@ -358,12 +359,86 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
           for (int e = 0; e < 32; ++e)
             if (pos0 + c * 32 + e > lim) sv[c][e] = 0xff800000u;     // -inf
       }
+      // P = exp2(S * scale - m) as bf16 / e4m3, written over the front of S; the row max of the tile (the
+      // max_score output, and what decides a rescale) is computed in the same pass.
+      // The special-function unit does 16 exp2 per clock per SM, a quarter of what the tensor pipe needs
+      // here, so kEmuMask selects pairs whose exp2 runs on the FMA pipe instead: round-to-nearest split
+      // x = n + f, degree-3 polynomial for 2^f (rel. error 7.5e-5, far below the rounding of P), n added
+      // into the exponent field.  All fp32 arithmetic is done on packed pairs (fma.rn.f32x2 / add.rn.f32x2).
       float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four independent chains
+      auto row_max = [&]() {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int e = 0; e < 32; e += 2)
-          mxs[(e >> 1) & 3] = max3(mxs[(e >> 1) & 3], __uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1]));
+          for (int e = 0; e < 32; e += 2)
+            mxs[(e >> 1) & 3] = max3(mxs[(e >> 1) & 3], __uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1]));
+      };
+      float l_rnd = 0.f, l_raw = 0.f;            // row sum of this tile: of P as stored / before rounding (e4m3)
+      auto emit_p = [&](auto with_max, const float m_ref) {
+        const uint64_t scale2 = f2_pack(scale_log2, scale_log2);
+        const uint64_t negm2 = f2_pack(-m_ref, -m_ref);
+        uint64_t lsum2 = f2_pack(0.f, 0.f), lex2 = f2_pack(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[F8 ? 8 : 16];
+          uint16_t held = 0;
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            if constexpr (decltype(with_max)::value)
+              mxs[(e >> 1) & 3] = max3(mxs[(e >> 1) & 3], __uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1]));
+            const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])), scale2, negm2);
+            float p0, p1;
+            if ((kEmuMask >> ((e >> 1) & 15)) & 1) {
+              float x0, x1;
+              f2_unpack(x2, x0, x1);
+              const uint64_t xc = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));     // also maps -inf
+              const uint64_t t2 = f2_add(xc, f2_pack(12582912.f, 12582912.f));          // 1.5 * 2^23: n in the low bits
+              const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
+              const uint64_t fr = f2_fma(n2, f2_pack(-1.f, -1.f), xc);                   // f in [-0.5, 0.5]
+              uint64_t pl = f2_fma(fr, f2_pack(0.055171650f, 0.055171650f), f2_pack(0.24261113f, 0.24261113f));
+              pl = f2_fma(pl, fr, f2_pack(0.69326097f, 0.69326097f));
+              pl = f2_fma(pl, fr, f2_pack(0.99992806f, 0.99992806f));
+              float q0, q1, t0, t1;
+              f2_unpack(pl, q0, q1);
+              f2_unpack(t2, t0, t1);
+              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+            } else {
+              float x0, x1;
+              f2_unpack(x2, x0, x1);
+              p0 = exp2_fast(x0);
+              p1 = exp2_fast(x1);
+            }
+            if constexpr (F8) {
+              // O is normalised by the sum of the probabilities as the MMA sees them (see the decode kernel);
+              // the LSE reports the sum before rounding
+              lex2 = f2_add(lex2, f2_pack(p0, p1));
+              const uint16_t pr = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
+              const float2 rr = e4m3x2_to_float2(pr);
+              lsum2 = f2_add(lsum2, f2_pack(rr.x, rr.y));
+              if (e & 2) pk[e >> 2] = static_cast<uint32_t>(held) | (static_cast<uint32_t>(pr) << 16);
+              else held = pr;
+            } else {
+              lsum2 = f2_add(lsum2, f2_pack(p0, p1));
+              pk[e >> 1] = pack2<false>(p0, p1);
+            }
+          }
+          if constexpr (F8) tmem_st8(tS + c * 8, pk);
+          else tmem_st16(tS + c * 16, pk);
+        }
+        float l0, l1;
+        f2_unpack(lsum2, l0, l1);
+        l_rnd = l0 + l1;
+        if constexpr (F8) { f2_unpack(lex2, l0, l1); l_raw = l0 + l1; }
+      };
+      // Every tile but the first writes P with the running max while it finds its own max: the max does
+      // not sit between the S read and the exponentials, and the guess holds unless the row's max grows
+      // by more than the rescale threshold (then P is written again below).
+      // (bf16 only: with e4m3 operands the kernel measured 6 % slower this way.)
+      const bool guess = !F8 && has_o && j > 0;                     // warp-uniform
+      const float m_guess = ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset;
+      if (guess) emit_p(std::true_type{}, m_guess);
+      else row_max();
       const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       if (want_score && row_ok && j < p.max_k_tiles) {
         const int64_t o = (static_cast<int64_t>(head) * p.max_k_tiles + j) * p.total_q + gtok;
@@ -377,83 +452,28 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       }
       // ---- running max with lazy rescale ----
       const float m_cand = fmaxf(m_used, mx * scale_log2);
-      const bool bump = (m_cand - m_used) > kRescaleThreshold;      // false for (-inf) - (-inf) = NaN
-      float factor = 1.f;
-      if (bump) { factor = exp2_fast(m_used - m_cand); m_used = m_cand; l_sum *= factor; l_exact *= factor; }
-      if (j > 0 && __any_sync(0xffffffffu, bump)) {
+      // false for (-inf) - (-inf) = NaN; true for a row whose first visible key is in this tile (its guess
+      // was made without a max)
+      const bool bump = (m_cand - m_used) > kRescaleThreshold;
+      if (!guess || __any_sync(0xffffffffu, bump)) {
+        float factor = 1.f;
+        if (bump) { factor = exp2_fast(m_used - m_cand); m_used = m_cand; l_sum *= factor; l_exact *= factor; }
+        if (j > 0 && __any_sync(0xffffffffu, bump)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tO + c * 32, v);
-          tmem_wait_ld();
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tO + c * 32, v);
+            tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
-          tmem_st32(tO + c * 32, v);
-        }
-      }
-      const float msafe = ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset;
-      if (r == 0) trace(x, j, 3);
-      // ---- P = exp2(S * scale - m) as bf16, written over the first half of S ----
-      // The special-function unit does 16 exp2 per clock per SM, a quarter of what the tensor
-      // pipe needs here, so kEmuMask selects pairs whose exp2 runs on the FMA pipe instead:
-      // round-to-nearest split x = n + f, degree-3 polynomial for 2^f (rel. error 7.5e-5, far
-      // below the bf16 rounding of P), n added into the exponent field.  All fp32 arithmetic
-      // is done on packed pairs (fma.rn.f32x2 / add.rn.f32x2).
-      const uint64_t scale2 = f2_pack(scale_log2, scale_log2);
-      const uint64_t negm2 = f2_pack(-msafe, -msafe);
-      uint64_t lsum2 = f2_pack(0.f, 0.f), lex2 = f2_pack(0.f, 0.f);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[F8 ? 8 : 16];
-        uint16_t held = 0;
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1])), scale2, negm2);
-          float p0, p1;
-          if ((kEmuMask >> ((e >> 1) & 15)) & 1) {
-            float x0, x1;
-            f2_unpack(x2, x0, x1);
-            const uint64_t xc = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));     // also maps -inf
-            const uint64_t t2 = f2_add(xc, f2_pack(12582912.f, 12582912.f));          // 1.5 * 2^23: n in the low bits
-            const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
-            const uint64_t fr = f2_fma(n2, f2_pack(-1.f, -1.f), xc);                   // f in [-0.5, 0.5]
-            uint64_t pl = f2_fma(fr, f2_pack(0.055171650f, 0.055171650f), f2_pack(0.24261113f, 0.24261113f));
-            pl = f2_fma(pl, fr, f2_pack(0.69326097f, 0.69326097f));
-            pl = f2_fma(pl, fr, f2_pack(0.99992806f, 0.99992806f));
-            float q0, q1, t0, t1;
-            f2_unpack(pl, q0, q1);
-            f2_unpack(t2, t0, t1);
-            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
-          } else {
-            float x0, x1;
-            f2_unpack(x2, x0, x1);
-            p0 = exp2_fast(x0);
-            p1 = exp2_fast(x1);
-          }
-          if constexpr (F8) {
-            // O is normalised by the sum of the probabilities as the MMA sees them (see the decode kernel);
-            // the LSE reports the sum before rounding
-            lex2 = f2_add(lex2, f2_pack(p0, p1));
-            const uint16_t pr = __nv_cvt_float2_to_fp8x2(make_float2(p0, p1), __NV_SATFINITE, __NV_E4M3);
-            const float2 rr = e4m3x2_to_float2(pr);
-            lsum2 = f2_add(lsum2, f2_pack(rr.x, rr.y));
-            if (e & 2) pk[e >> 2] = static_cast<uint32_t>(held) | (static_cast<uint32_t>(pr) << 16);
-            else held = pr;
-          } else {
-            lsum2 = f2_add(lsum2, f2_pack(p0, p1));
-            pk[e >> 1] = pack2<false>(p0, p1);
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+            tmem_st32(tO + c * 32, v);
           }
         }
-        if constexpr (F8) tmem_st8(tS + c * 8, pk);
-        else tmem_st16(tS + c * 16, pk);
+        if (r == 0) trace(x, j, 3);
+        emit_p(std::false_type{}, ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset);
       }
-      {
-        float l0, l1;
-        f2_unpack(lsum2, l0, l1);
-        l_sum += l0 + l1;
-        if constexpr (F8) { f2_unpack(lex2, l0, l1); l_exact += l0 + l1; }
-      }
+      l_sum += l_rnd;
+      if constexpr (F8) l_exact += l_raw;
       if (r == 0) trace(x, j, 4);
       tmem_wait_st();
       tc_fence_before();
