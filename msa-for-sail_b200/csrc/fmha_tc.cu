@@ -42,7 +42,7 @@ constexpr int BN = 128;                 // keys per KV tile
 constexpr int SUB_BYTES = BM * 128;     // one [128 rows][128 bytes] swizzled sub-tile: 64 bf16 or 128 e4m3 per row
 constexpr int NTHREADS = 384;
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
-constexpr uint32_t kEmuMask = 0x5252;              // pairs (of 16 per 32 columns) whose exp2 is computed on the FMA pipe
+constexpr uint32_t kEmuMask = 0x1111;              // pairs (of 16 per 32 columns) whose exp2 is computed on the FMA pipe
 
 // F8: Q, K, V (and P) are e4m3 and the MMAs are kind::f8f6f4; otherwise bf16 and kind::f16.  A tile is
 // half as large in e4m3, so the K and V rings are twice as deep in the same shared memory.
@@ -381,7 +381,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[F8 ? 8 : 16];
-          uint16_t held = 0;
+          [[maybe_unused]] uint16_t held = 0;
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             if constexpr (decltype(with_max)::value)
