@@ -67,11 +67,13 @@ score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
   const int b = chk(w.batch, 0, p.batch, p.status), head0 = chk(w.head0, 0, p.num_qo_heads, p.status);
   const int h_r = p.num_qo_heads / p.num_kv_heads;
   const int kvh = head0 / h_r, G = p.pack;
-  const int qo_base = p.qo_start[b];
-  // rows of this item; a batch slot without query tokens (graph-safe padding) is an empty item
-  const int nrows = min((p.qo_start[b + 1] - qo_base) * G, w.num_rows);
-  if (nrows <= 0) return;                          // uniform for the CTA; nothing below is shared
+  // (all of the item's metadata is requested before the first use: one round trip, not two)
+  const int qo_base = p.qo_start[b], qo_end = p.qo_start[b + 1];
   const int kv_len = p.kv_len[b], off = p.qo_offset[b], page_base = p.kv_page_indptr[b];
+  // rows of this item; a batch slot without query tokens (graph-safe padding) is an empty item: it loads the
+  // (clamped, hence valid) first row of Q and walks no tile.  (An early return instead measured 3 % slower
+  // on the whole pass.)
+  const int nrows = min((qo_end - qo_base) * G, w.num_rows);
   const int c = lane % L, ksub = lane / L;
 
   // this lane's slice of every row of Q
@@ -79,8 +81,8 @@ score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
   int lim[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int rr = min(r, nrows - 1);
-    const int gtok = qo_base + rr / G, head = head0 + rr % G;
+    const int rr = max(0, min(r, nrows - 1));
+    const int gtok = max(0, min(qo_base + rr / G, p.total_q - 1)), head = head0 + rr % G;
     lim[r] = r < nrows ? min(rr / G + off, kv_len - 1) : -1;
     if (p.q_dtype == MSA_DT_E4M3) {
       const uint4 v = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.q) +
@@ -113,7 +115,8 @@ score_gemv_kernel(const __grid_constant__ MsaFmhaParams p) {
                                static_cast<int64_t>(ksub) * p.k_stride_tok * e + c * 16;
   const int64_t load_step = static_cast<int64_t>(KPL) * p.k_stride_tok * e;     // bytes between a lane's loads
   const int stride = gridDim.x * NWARPS;
-  for (int t = w.kv_tile_begin + blockIdx.x * NWARPS + warp; t < w.kv_tile_end; t += stride) {
+  const int t_end = nrows > 0 ? w.kv_tile_end : w.kv_tile_begin;
+  for (int t = w.kv_tile_begin + blockIdx.x * NWARPS + warp; t < t_end; t += stride) {
     const int phys = chk(p.kv_indices[page_base + t], 0, static_cast<int>(p.kv_extent), p.status);
     const unsigned char* kp = kbase + static_cast<int64_t>(phys) * p.k_stride_page * e;
     float mx[R];
