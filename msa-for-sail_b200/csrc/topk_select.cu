@@ -32,30 +32,14 @@ __device__ __forceinline__ uint32_t ord_key(float v) {
   return v != v ? 0xFFFFFFFFu : key;
 }
 
-// Keys of the thread-per-row kernel.  64-bit integer compares and selects run on a quarter-rate pipe on
-// sm_100 (a version of this kernel on (order key << 32 | ~page) words spent 65 % of its time there), so the
-// compare-exchange networks work on 32-bit registers only:
-//   Key2  an (order key, page) pair compared as (key desc, page asc): 3 compares + 4 selects per exchange;
-//   Key1  bf16 scores: the upper half of the order key is exact for them, so (key16 << 16 | ~page16) is one
-//         32-bit word and an exchange is one max and one min.  Not used with forced pages, which rank as the
-//         fp32 maximum -- a score bf16 cannot tell from its own largest finite value -- nor beyond 65 535 pages.
-// Keys are unique (the page is part of them), hence a strict total order: no tie handling anywhere.
-struct Key2 {
-  uint32_t o, i;
-  static __device__ __forceinline__ Key2 none() { return {0u, 0xffffffffu}; }            // below every real key
-  static __device__ __forceinline__ Key2 make(uint32_t ord, int page) { return {ord, static_cast<uint32_t>(page)}; }
-  __device__ __forceinline__ bool is_none() const { return o == 0u; }
-  __device__ __forceinline__ uint32_t page() const { return i; }
-  static __device__ __forceinline__ void order(Key2& a, Key2& b) {                        // a ranks before b afterwards
-    const bool sw = b.o > a.o || (b.o == a.o && b.i < a.i);
-    const Key2 hi = {sw ? b.o : a.o, sw ? b.i : a.i}, lo = {sw ? a.o : b.o, sw ? a.i : b.i};
-    a = hi; b = lo;
-  }
-  static __device__ __forceinline__ Key2 best(const Key2& a, const Key2& b) {
-    const bool sw = b.o > a.o || (b.o == a.o && b.i < a.i);
-    return {sw ? b.o : a.o, sw ? b.i : a.i};
-  }
-};
+// Keys of the thread-per-row kernel.  Keys are unique (the page is part of them), hence a strict total order:
+// no tie handling anywhere.
+//   Key64  (order key << 32 | ~page) in one 64-bit word: a compare-exchange is one 64-bit compare and two
+//          64-bit selects.  (An (order key, page) pair in two 32-bit registers, 3 compares + 4 selects per
+//          exchange, measured 116-121 us against 101 us at 65 536 rows x 256 pages of fp32 scores.)
+//   Key1   bf16 scores: the upper half of the order key is exact for them, so (key16 << 16 | ~page16) is one
+//          32-bit word and an exchange is one max and one min.  Not used with forced pages, which rank as the
+//          fp32 maximum -- a score bf16 cannot tell from its own largest finite value -- nor beyond 65 535 pages.
 struct Key1 {
   uint32_t k;
   static __device__ __forceinline__ Key1 none() { return {0u}; }
@@ -69,6 +53,22 @@ struct Key1 {
     a.k = hi; b.k = lo;
   }
   static __device__ __forceinline__ Key1 best(const Key1& a, const Key1& b) { return {max(a.k, b.k)}; }
+};
+
+struct Key64 {
+  unsigned long long k;
+  static __device__ __forceinline__ Key64 none() { return {0ull}; }
+  static __device__ __forceinline__ Key64 make(uint32_t ord, int page) {
+    return {(static_cast<unsigned long long>(ord) << 32) | (0xffffffffu - static_cast<uint32_t>(page))};
+  }
+  __device__ __forceinline__ bool is_none() const { return (k >> 32) == 0ull; }
+  __device__ __forceinline__ uint32_t page() const { return 0xffffffffu - static_cast<uint32_t>(k); }
+  static __device__ __forceinline__ void order(Key64& a, Key64& b) {
+    const bool sw = b.k > a.k;
+    const unsigned long long hi = sw ? b.k : a.k, lo = sw ? a.k : b.k;
+    a.k = hi; b.k = lo;
+  }
+  static __device__ __forceinline__ Key64 best(const Key64& a, const Key64& b) { return {b.k > a.k ? b.k : a.k}; }
 };
 
 // descending bitonic sort of N keys / merge of a descending list into the sorted top-N list (static
@@ -297,14 +297,14 @@ int launch(const T* scores, int32_t* out, int H, int K, int T_, int nvp, int fb,
   while (slices < 8 && ctas * slices < 148LL * 16 && nvp / (slices * 2) >= 2 * TOPK) slices *= 2;
   if (ctas > 0x7fffffffLL) return MSA_ERR_TOO_LARGE;
   const bool one_word = sizeof(T) == 2 && fb == 0 && fe == 0 && nvp <= 65535;      // bf16 scores, nothing forced
-  const size_t smem = slices > 1 ? static_cast<size_t>(slices) * 32 * TOPK * (one_word ? sizeof(Key1) : sizeof(Key2)) : 0;
+  const size_t smem = slices > 1 ? static_cast<size_t>(slices) * 32 * TOPK * (one_word ? sizeof(Key1) : sizeof(Key64)) : 0;
   const unsigned grid = static_cast<unsigned>(ctas);
   if (one_word) {
     auto kern = topk_select_kernel<TOPK, T, Key1>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, 32 * slices, smem, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start, slices);
   } else {
-    auto kern = topk_select_kernel<TOPK, T, Key2>;
+    auto kern = topk_select_kernel<TOPK, T, Key64>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, 32 * slices, smem, stream>>>(scores, out, H, K, T_, nvp, fb, fe_start, slices);
   }
