@@ -359,6 +359,25 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
           for (int e = 0; e < 32; ++e)
             if (pos0 + c * 32 + e > lim) sv[c][e] = 0xff800000u;     // -inf
       }
+      auto store_score = [&](const float mx) {
+        if (want_score && row_ok && j < p.max_k_tiles) {
+          const int64_t o = (static_cast<int64_t>(head) * p.max_k_tiles + j) * p.total_q + gtok;
+          if (p.max_score_dtype == MSA_DT_BF16) static_cast<__nv_bfloat16*>(p.max_score)[o] = __float2bfloat16_rn(mx);
+          else static_cast<float*>(p.max_score)[o] = mx;
+        }
+      };
+      if (!has_o) {                    // score-only pass: the row max of the tile, then S goes back to the MMA warp
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};        // four independent chains
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; e += 2)
+            m4[(e >> 1) & 3] = max3(m4[(e >> 1) & 3], __uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1]));
+        store_score(fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+        tc_fence_before();
+        mbar_arrive(bar(P_FULL + x));
+        continue;
+      }
       // P = exp2(S * scale - m) as bf16 / e4m3, written over the front of S; the row max of the tile (the
       // max_score output, and what decides a rescale) is computed in the same pass.
       // The special-function unit does 16 exp2 per clock per SM, a quarter of what the tensor pipe needs
@@ -435,21 +454,12 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
       // not sit between the S read and the exponentials, and the guess holds unless the row's max grows
       // by more than the rescale threshold (then P is written again below).
       // (bf16 only: with e4m3 operands the kernel measured 6 % slower this way.)
-      const bool guess = !F8 && has_o && j > 0;                     // warp-uniform
+      const bool guess = !F8 && j > 0;                              // warp-uniform
       const float m_guess = ((m_used == -INFINITY) ? 0.f : m_used) - kPOffset;
       if (guess) emit_p(std::true_type{}, m_guess);
       else row_max();
       const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-      if (want_score && row_ok && j < p.max_k_tiles) {
-        const int64_t o = (static_cast<int64_t>(head) * p.max_k_tiles + j) * p.total_q + gtok;
-        if (p.max_score_dtype == MSA_DT_BF16) static_cast<__nv_bfloat16*>(p.max_score)[o] = __float2bfloat16_rn(mx);
-        else static_cast<float*>(p.max_score)[o] = mx;
-      }
-      if (!has_o) {                    // score-only pass: S is consumed, hand the buffer back
-        tc_fence_before();
-        mbar_arrive(bar(P_FULL + x));
-        continue;
-      }
+      store_score(mx);
       // ---- running max with lazy rescale ----
       const float m_cand = fmaxf(m_used, mx * scale_log2);
       // false for (-inf) - (-inf) = NaN; true for a row whose first visible key is in this tile (its guess
