@@ -78,7 +78,9 @@ struct Knobs {            // read only in builds with -DMSA_DEBUG_HOOKS
   uint32_t spin_limit;         // > 0: polls a bounded wait makes before it gives up (instead of kSpinLimit)
 };
 
-template <bool F8>
+// HAS_O = false: score-only pass (no V, no P, no O), compiled on its own so that neither path's code is shaped
+// by the other's.
+template <bool F8, bool HAS_O>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ CUtensorMap tm_q,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -121,7 +123,7 @@ fmha_tc_kernel(const __grid_constant__ MsaFmhaParams p, const __grid_constant__ 
   const int kv_len = p.kv_len[b];
   const int off = p.qo_offset[b];
   const bool paged = p.page_size > 0;
-  const bool has_o = (p.flags & MSA_FLAG_OUT_O) != 0;     // false: score-only pass, no V, no P, no O
+  constexpr bool has_o = HAS_O;
   int n_tiles[2];
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
@@ -631,19 +633,20 @@ int fmha_tc_launch(const MsaFmhaParams& p, cudaStream_t stream) {
     if (!make_map(&tk, p.k, 3, dims, ks, box, f8) || !make_map(&tv, has_o ? p.v : p.k, 3, dims, has_o ? vs : ks, box, f8))
       return MSA_ERR_LAUNCH;
   }
-  static bool attr_done[2][16] = {};
+  static bool attr_done[4][16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 16 || !attr_done[f8][dev]) {
-    const cudaError_t e = f8 ? cudaFuncSetAttribute(fmha_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    Cfg<true>::SMEM_BYTES)
-                             : cudaFuncSetAttribute(fmha_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    Cfg<false>::SMEM_BYTES);
-    if (e != cudaSuccess) return MSA_ERR_LAUNCH;
-    if (dev < 16) attr_done[f8][dev] = true;
+  using KernelFn = void (*)(const MsaFmhaParams, const CUtensorMap, const CUtensorMap, const CUtensorMap, const Knobs);
+  const int variant = (f8 ? 2 : 0) | (has_o ? 1 : 0);
+  const KernelFn kernels[4] = {fmha_tc_kernel<false, false>, fmha_tc_kernel<false, true>, fmha_tc_kernel<true, false>,
+                               fmha_tc_kernel<true, true>};
+  const KernelFn kern = kernels[variant];
+  const int smem_bytes = f8 ? Cfg<true>::SMEM_BYTES : Cfg<false>::SMEM_BYTES;
+  if (dev >= 16 || !attr_done[variant][dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return MSA_ERR_LAUNCH;
+    if (dev < 16) attr_done[variant][dev] = true;
   }
-  if (f8) fmha_tc_kernel<true><<<p.num_work, NTHREADS, Cfg<true>::SMEM_BYTES, stream>>>(p, tq, tk, tv, g_knobs);
-  else fmha_tc_kernel<false><<<p.num_work, NTHREADS, Cfg<false>::SMEM_BYTES, stream>>>(p, tq, tk, tv, g_knobs);
+  kern<<<p.num_work, NTHREADS, smem_bytes, stream>>>(p, tq, tk, tv, g_knobs);
   return cudaGetLastError() == cudaSuccess ? MSA_OK : MSA_ERR_LAUNCH;
 }
 
